@@ -1,0 +1,163 @@
+/*
+ * pith_b200 — C ABI of the sm_100a context-parallel attention path.
+ *
+ * The library replaces the arithmetic behind PithTrain's ring-attention operators
+ * (pithtrain/operators/ring_attention/standard.py, pithtrain/operators/ring_attention/mla.py,
+ * pithtrain/operators/mla/triton.py). The reference has no foreign-function boundary of its
+ * own: its operators call flash-attn and Triton kernels from Python. Each entry point below
+ * names the reference call it stands in for.
+ *
+ * Conventions
+ *  - Every buffer is device memory owned by the caller; the library allocates nothing and
+ *    keeps no pointer after the call returns. Calls only enqueue work on `stream`.
+ *  - Tensors are [B][S][H][D] with the innermost dimension contiguous; strides are given in
+ *    ELEMENTS for the b, s and h dimensions. Base pointers and (stride * element size) must
+ *    be multiples of 16 bytes. bf16 unless stated.
+ *  - LSE / delta tensors are fp32 [B][H][S] with unit stride along S; their b and h strides
+ *    are given in elements.
+ *  - Return value: 0 = enqueued; negative = rejected on the host (pith_last_error() has the
+ *    text). Device-side anomalies (a bounded wait that ran out) are written to *status
+ *    (a zero-initialised device uint32, optional) as (code << 24 | detail); see pith_status_string.
+ *  - Re-entrant; no internal threads; no global mutable state besides a cache of TMA descriptors.
+ */
+#ifndef PITH_B200_H_
+#define PITH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PITH_B200_ABI_VERSION 1
+
+/* flags for pith_attn_fwd_args.flags */
+#define PITH_FWD_O_FP32 1u        /* `o` is fp32 (running accumulator of a ring) instead of bf16 */
+#define PITH_FWD_LSE_NATURAL 2u   /* write natural-log LSE (flash-attn convention) instead of log2 */
+
+/* flags for pith_combine_args.flags */
+#define PITH_COMBINE_NATURAL 1u   /* LSEs are natural-log (standard.py) instead of log2 (mla.py) */
+
+/* element types for pith_combine_args.out*_dtype */
+#define PITH_DTYPE_BF16 0
+#define PITH_DTYPE_F32 1
+
+typedef struct pith_attn_fwd_args {
+  const void* q;          /* [B][Sq][Hq][Dqk] bf16 */
+  const void* k;          /* [B][Sk][Hkv][Dqk] bf16 */
+  const void* v;          /* [B][Sk][Hkv][Dv] bf16 */
+  void* o;                /* [B][Sq][Hq][Dv] bf16, or fp32 with PITH_FWD_O_FP32 */
+  float* lse;             /* [B][Hq][Sq] */
+  const float* prev_o;    /* optional fp32 [B][Sq][Hq][Dv]: partial result to merge in the epilogue */
+  const float* prev_lse;  /* optional fp32 [B][Hq][Sq], log2 domain, paired with prev_o */
+  float* debug;           /* optional; internal bring-up dumps (3 * 128 * 128 + 256 floats) */
+  uint32_t* status;       /* optional device status word */
+  int32_t B, Sq, Sk, Hq, Hkv, Dqk, Dv;
+  int32_t causal;         /* 0 = every key visible; 1 = key n visible to query m iff n <= m + causal_offset */
+  int32_t causal_offset;
+  uint32_t flags;
+  float softmax_scale;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], prev_o_stride[3]; /* b, s, h (elements) */
+  int64_t lse_stride[2], prev_lse_stride[2];                                    /* b, h (elements) */
+} pith_attn_fwd_args;
+
+/*
+ * Causal / non-causal attention forward for one (Q block, KV block) pair, GQA (Dqk = Dv = 128)
+ * or MLA (Dqk = 192, Dv = 128), with log2-domain LSE and an optional fused online-softmax
+ * merge with a previous partial (O, LSE).
+ * Replaces: flash_attn `_flash_attn_forward` as called at
+ *   pithtrain/operators/ring_attention/standard.py:91-93, `flash_attn_func` at
+ *   pithtrain/models/qwen3_30b_a3b.py:424, and `_mla_fwd` (pithtrain/operators/mla/triton.py:552-563)
+ *   as called at pithtrain/operators/ring_attention/mla.py:67; with prev_o/prev_lse it also covers
+ *   the combine at standard.py:94 / mla.py:68.
+ */
+int pith_attn_fwd(const pith_attn_fwd_args* args, void* stream);
+
+typedef struct pith_bwd_preprocess_args {
+  const void* o;    /* [B][S][H][Dv] bf16 */
+  const void* dout; /* [B][S][H][Dv] bf16 */
+  float* delta;     /* [B][H][S] fp32 = rowsum(o * dout) */
+  int32_t B, S, H, Dv;
+  int64_t o_stride[3], do_stride[3];
+  int64_t delta_stride[2];
+} pith_bwd_preprocess_args;
+
+/*
+ * delta = rowsum(O * dO).
+ * Replaces: `_mla_bwd_preprocess` (pithtrain/operators/mla/triton.py:566-574, kernel :99-122),
+ *   called once per backward at pithtrain/operators/ring_attention/mla.py:101; flash-attn computes
+ *   the same quantity inside `_flash_attn_backward` (standard.py:134-153).
+ */
+int pith_attn_bwd_preprocess(const pith_bwd_preprocess_args* args, void* stream);
+
+typedef struct pith_attn_bwd_args {
+  const void* q;      /* [B][Sq][Hq][Dqk] bf16 */
+  const void* k;      /* [B][Sk][Hkv][Dqk] bf16 */
+  const void* v;      /* [B][Sk][Hkv][Dv] bf16 */
+  const void* dout;   /* [B][Sq][Hq][Dv] bf16 */
+  const float* lse;   /* [B][Hq][Sq] fp32, log2 domain, of the COMPLETE softmax row */
+  const float* delta; /* [B][Hq][Sq] fp32 */
+  float* dq_acc;      /* [B][Sq][Hq][Dqk] fp32, accumulated into (+=) */
+  float* dk_acc;      /* [B][Sk][Hkv][Dqk] fp32, accumulated into (+=) */
+  float* dv_acc;      /* [B][Sk][Hkv][Dv] fp32, accumulated into (+=) */
+  uint32_t* status;
+  float* debug;
+  int32_t B, Sq, Sk, Hq, Hkv, Dqk, Dv;
+  int32_t causal, causal_offset;
+  uint32_t flags;
+  float softmax_scale;
+  int64_t q_stride[3], k_stride[3], v_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+  int64_t lse_stride[2], delta_stride[2];
+} pith_attn_bwd_args;
+
+/*
+ * dQ, dK, dV contributions of one (Q block, KV block) pair, added into fp32 accumulators so that
+ * a ring of steps (and the query heads of one GQA group) round to bf16 once, at the end.
+ * Replaces: `_flash_attn_backward` as called at pithtrain/operators/ring_attention/standard.py:134-153
+ *   together with the `dq += dq_s` / `local_dk += ...` updates at :154-160,:185-187; and
+ *   `_mla_bwd_dk_dv` + `_mla_bwd_dq` (pithtrain/operators/mla/triton.py:577-603) as called at
+ *   pithtrain/operators/ring_attention/mla.py:110-115.
+ */
+int pith_attn_bwd(const pith_attn_bwd_args* args, void* stream);
+
+/*
+ * out_bf16[i] = (bf16) acc_f32[i] * scale for a [B][S][H][D] tensor (final rounding of an accumulator).
+ * Replaces: the `.to(q.dtype)` at standard.py:104 / mla.py:78 and the implicit bf16 rounding of
+ *   flash-attn / Triton gradient outputs.
+ */
+int pith_cast_f32_to_bf16(const float* acc, void* out, int32_t B, int32_t S, int32_t H, int32_t D,
+                          const int64_t acc_stride[3], const int64_t out_stride[3], float scale, void* stream);
+
+typedef struct pith_combine_args {
+  const void* out1;  /* [B][S][H][D] */
+  const float* lse1; /* [B][H][S] */
+  const void* out2;
+  const float* lse2;
+  float* out;        /* [B][S][H][D] fp32, contiguous */
+  float* lse;        /* [B][H][S] fp32, contiguous */
+  int32_t out1_dtype, out2_dtype; /* PITH_DTYPE_* */
+  int32_t B, S, H, D;
+  uint32_t flags;
+  int64_t out1_stride[3], out2_stride[3];
+  int64_t lse1_stride[2], lse2_stride[2];
+} pith_combine_args;
+
+/*
+ * Online-softmax merge of two partial attention results.
+ * Replaces: `_online_softmax_combine` (pithtrain/operators/ring_attention/standard.py:53-66) and
+ *   `_online_softmax_combine_log2` (pithtrain/operators/ring_attention/mla.py:27-40).
+ */
+int pith_combine(const pith_combine_args* args, void* stream);
+
+/* Text of the last host-side rejection on the calling thread. */
+const char* pith_last_error(void);
+/* Human-readable form of a device status word. Returns a pointer to a thread-local buffer. */
+const char* pith_status_string(uint32_t status);
+int pith_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PITH_B200_H_ */

@@ -1,0 +1,433 @@
+// Attention forward for sm_100a: S = Q K^T and O += P V run on tcgen05 with fp32 accumulators
+// in TMEM; Q/K/V tiles arrive through TMA into 128-byte-swizzled shared memory.
+//
+// One CTA owns two 128-row query tiles of one (batch, query head) and walks the key/value
+// blocks they need. Warp roles (384 threads):
+//   warp 0        TMA producer: Q once, then K and V blocks through KST / VST-deep rings
+//   warp 1        tcgen05 issuer (one lane): S_t = Q_t K_j^T, O_t += P_t V_j
+//   warps 4..7    softmax group of tile 0, one thread per query row (= TMEM lane)
+//   warps 8..11   softmax group of tile 1
+// The two softmax groups alternate with the tensor core: while group 0 turns S_0 into P_0
+// the tensor core works on tile 1 and vice versa.
+//
+// TMEM columns (512, fp32): [0,128) S_0 (P_0 packed bf16 overlays [0,64)), [128,256) S_1 / P_1,
+// [256,384) O_0, [384,512) O_1.
+//
+// Softmax runs in the exp2 domain; the running maximum is only moved when it grows by more than
+// 2^8 (warp-uniform decision), which keeps the O rescale off the common path. The epilogue
+// normalises, optionally merges a previous partial (O, LSE) (the ring's online-softmax combine)
+// and writes bf16 or fp32 O plus the log2-domain LSE.
+#include "../../include/pith_b200.h"
+#include "common.cuh"
+#include "host_common.h"
+
+namespace pith {
+
+struct FwdParams {
+  void* o;
+  float* lse;
+  const float* prev_o;
+  const float* prev_lse;
+  float* dbg;
+  uint32_t* status;
+  int B, Sq, Sk, Hq, Hkv;
+  int causal, causal_off;
+  int o_fp32, lse_natural;
+  float scale_log2;
+  int64_t os[3], pos[3];
+  int64_t ls[2], pls[2];
+};
+
+constexpr int kFwdThreads = 384;
+constexpr int kBM = 128;  // query rows per tile
+constexpr int kDV = 128;
+
+template <int DQK, int BN, int KST, int VST>
+struct FwdSmem {
+  static constexpr int kQTile = kBM * DQK * 2;  // bytes of one Q tile
+  static constexpr int kKTile = BN * DQK * 2;
+  static constexpr int kVTile = BN * kDV * 2;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + 2 * kQTile;
+  static constexpr int kVOff = kKOff + KST * kKTile;
+  static constexpr int kBarOff = kVOff + VST * kVTile;
+  static constexpr int kNumBars = 1 + 2 * KST + 2 * VST + 6;
+  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+  static constexpr int kAlloc = kTotal + 1024;  // slack for the 1024-byte alignment of the base
+};
+
+// S[128 x BN] = Q_tile[128 x DQK] * K_blk[BN x DQK]^T, both operands K-major in shared memory.
+template <int DQK, int BN>
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t sq, uint32_t sk, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < DQK / 16; ++kk) {
+    const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
+    const uint64_t a = make_smem_desc(sq + sub * (kBM * 128) + off, 16, 1024);
+    const uint64_t b = make_smem_desc(sk + sub * (BN * 128) + off, 16, 1024);
+    umma_ss(d_tmem, a, b, idesc, kk > 0 ? 1u : 0u);
+  }
+}
+
+// O[128 x 128] (+)= P[128 x BN] (bf16 in TMEM) * V_blk[BN x 128] (MN-major in shared memory:
+// two [BN][64] column blocks, BN * 128 bytes apart).
+template <int BN>
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t sv, uint32_t idesc, bool acc) {
+#pragma unroll
+  for (int kk = 0; kk < BN / 16; ++kk) {
+    const uint64_t b = make_smem_desc(sv + kk * 2048, BN * 128, 1024);
+    umma_ts(d_tmem, p_tmem + kk * 8, b, idesc, (acc || kk > 0) ? 1u : 0u);
+  }
+}
+
+template <int DQK, int BN, int KST, int VST>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+    attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using L = FwdSmem<DQK, BN, KST, VST>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::kQOff;
+  uint8_t* sK = smem + L::kKOff;
+  uint8_t* sV = smem + L::kVOff;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = k_full + KST;
+  uint64_t* v_full = k_empty + KST;
+  uint64_t* v_empty = v_full + VST;
+  uint64_t* s_full = v_empty + VST;  // [2]
+  uint64_t* p_full = s_full + 2;     // [2]
+  uint64_t* o_full = p_full + 2;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const AbortCtl ctl{p.status, abort_flag};
+
+  // Heaviest (latest) query tiles first.
+  const int qblk = gridDim.x - 1 - blockIdx.x;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.Hq / p.Hkv);
+  const int m0 = qblk * (2 * kBM);
+
+  int nblk[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int lo = m0 + t * kBM;
+    int kv_end = p.Sk;
+    if (p.causal) {
+      const int hi = min(lo + kBM - 1, p.Sq - 1);
+      kv_end = min(p.Sk, hi + p.causal_off + 1);
+    }
+    nblk[t] = (lo < p.Sq && kv_end > 0) ? (kv_end + BN - 1) / BN : 0;
+  }
+  const int nmax = max(nblk[0], nblk[1]);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0u;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < KST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
+    for (int i = 0; i < VST; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && nmax > 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_arrive_expect_tx(q_full, 2 * L::kQTile);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int sub = 0; sub < DQK / 64; ++sub)
+          tma_load_4d(sQ + t * L::kQTile + sub * (kBM * 128), &tm_q, q_full, sub * 64, head, m0 + t * kBM, batch);
+      for (int j = 0; j < nmax; ++j) {
+        const int ks = j % KST, vs = j % VST;
+        mbar_wait(&k_empty[ks], ((j / KST) & 1) ^ 1, ctl, 0x100 + ks);
+        mbar_arrive_expect_tx(&k_full[ks], L::kKTile);
+#pragma unroll
+        for (int sub = 0; sub < DQK / 64; ++sub)
+          tma_load_4d(sK + ks * L::kKTile + sub * (BN * 128), &tm_k, &k_full[ks], sub * 64, kv_head, j * BN, batch);
+        mbar_wait(&v_empty[vs], ((j / VST) & 1) ^ 1, ctl, 0x200 + vs);
+        mbar_arrive_expect_tx(&v_full[vs], L::kVTile);
+#pragma unroll
+        for (int sub = 0; sub < kDV / 64; ++sub)
+          tma_load_4d(sV + vs * L::kVTile + sub * (BN * 128), &tm_v, &v_full[vs], sub * 64, kv_head, j * BN, batch);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && nmax > 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(kBM, BN, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, kDV, false, true);
+      const uint32_t sq = smem_u32(sQ), sk = smem_u32(sK), sv = smem_u32(sV);
+      mbar_wait(q_full, 0, ctl, 0x300);
+      mbar_wait(&k_full[0], 0, ctl, 0x400);
+      tc_fence_after_sync();
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (nblk[t] > 0) {
+          issue_qk<DQK, BN>(tmem_base + t * 128, sq + t * L::kQTile, sk, idesc_qk);
+          umma_commit(&s_full[t]);
+        }
+      }
+      umma_commit(&k_empty[0]);
+      for (int j = 0; j < nmax; ++j) {
+        const int vs = j % VST;
+        const bool have_next = j + 1 < nmax;
+        const int ks = (j + 1) % KST;
+        mbar_wait(&v_full[vs], (j / VST) & 1, ctl, 0x500 + vs);
+        if (have_next) mbar_wait(&k_full[ks], ((j + 1) / KST) & 1, ctl, 0x400 + ks);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < nblk[t]) {
+            mbar_wait(&p_full[t], j & 1, ctl, 0x600 + t);
+            tc_fence_after_sync();
+            issue_pv<BN>(tmem_base + 256 + t * 128, tmem_base + t * 128, sv + vs * L::kVTile, idesc_pv, j > 0);
+            if (j + 1 < nblk[t]) {
+              issue_qk<DQK, BN>(tmem_base + t * 128, sq + t * L::kQTile, sk + ks * L::kKTile, idesc_qk);
+              umma_commit(&s_full[t]);
+            } else {
+              umma_commit(&o_full[t]);
+            }
+          }
+        }
+        umma_commit(&v_empty[vs]);
+        if (have_next) umma_commit(&k_empty[ks]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 4) >> 2;                 // query tile of this warpgroup
+    const int row_in_tile = ((warp & 3) << 5) + lane;  // TMEM lane == query row
+    const int row = m0 + t * kBM + row_in_tile;    // query position inside this call's Q block
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
+    const uint32_t tS = tmem_base + lane_addr + t * 128;
+    const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
+    const float c = p.scale_log2;
+    const int nb = nblk[t];
+    const bool dump = p.dbg != nullptr && blockIdx.x == gridDim.x - 1 && head == 0 && batch == 0 && t == 0;
+
+    float m_used = -INFINITY;
+    float l = 0.f;
+    for (int j = 0; j < nb; ++j) {
+      mbar_wait(&s_full[t], j & 1, ctl, 0x700 + t);
+      tc_fence_after_sync();
+      uint32_t sr[BN];
+#pragma unroll
+      for (int cchunk = 0; cchunk < BN / 32; ++cchunk) tmem_ld32(tS + cchunk * 32, sr + cchunk * 32);
+      tmem_wait_ld();
+      if (dump && j == 0) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) p.dbg[row_in_tile * 128 + i] = __uint_as_float(sr[i]);
+      }
+      const int n0 = j * BN;
+      const bool need_mask = (p.causal && (n0 + BN - 1 > m0 + t * kBM + p.causal_off)) || (n0 + BN > p.Sk);
+      if (need_mask) {
+        const int limit = p.causal ? min(p.Sk - 1, row + p.causal_off) : p.Sk - 1;  // last visible key
+#pragma unroll
+        for (int i = 0; i < BN; ++i)
+          if (n0 + i > limit) sr[i] = 0xFF800000u;  // -inf
+      }
+      float m_blk = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BN; ++i) m_blk = fmaxf(m_blk, __uint_as_float(sr[i]));
+      const float m_new = fmaxf(m_used, m_blk);
+      if (j == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = (m_new - m_used) * c > 8.0f;
+        if (__any_sync(0xFFFFFFFFu, need)) {
+          const float alpha = need ? fast_exp2((m_used - m_new) * c) : 1.0f;
+          if (need) m_used = m_new;
+          l *= alpha;
+#pragma unroll
+          for (int cchunk = 0; cchunk < kDV / 32; ++cchunk) {
+            uint32_t orr[32];
+            tmem_ld32(tO + cchunk * 32, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+            tmem_st32(tO + cchunk * 32, orr);
+          }
+        }
+      }
+      const float mc = (m_used == -INFINITY) ? 0.f : m_used * c;
+      float lsum = 0.f;
+#pragma unroll
+      for (int cchunk = 0; cchunk < BN / 64; ++cchunk) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cchunk * 64 + 2 * i]), c, -mc));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cchunk * 64 + 2 * i + 1]), c, -mc));
+          lsum += p0 + p1;
+          pk[i] = pack_bf16(p0, p1);
+          if (dump && j == 0) {
+            p.dbg[16384 + row_in_tile * 128 + cchunk * 64 + 2 * i] = p0;
+            p.dbg[16384 + row_in_tile * 128 + cchunk * 64 + 2 * i + 1] = p1;
+          }
+        }
+        tmem_st32(tS + cchunk * 32, pk);
+      }
+      l += lsum;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[t]);
+    }
+
+    // ---- epilogue: normalise, optional merge with a previous partial, store
+    if (nb > 0) {
+      mbar_wait(&o_full[t], 0, ctl, 0x800 + t);
+      tc_fence_after_sync();
+    }
+    const bool row_ok = row < p.Sq;
+    float inv = (l > 0.f) ? 1.0f / l : 0.f;
+    float lse2 = (l > 0.f) ? fmaf(m_used, c, fast_log2(l)) : -INFINITY;
+    if (dump) {
+      p.dbg[3 * 16384 + 2 * row_in_tile] = m_used;
+      p.dbg[3 * 16384 + 2 * row_in_tile + 1] = l;
+    }
+    float w_prev = 0.f;
+    if (p.prev_o != nullptr) {
+      const float pl = row_ok ? p.prev_lse[batch * p.pls[0] + head * p.pls[1] + row] : -INFINITY;
+      const float mx = fmaxf(pl, lse2);
+      if (mx > -INFINITY) {
+        const float e1 = exp2f(pl - mx), e2 = exp2f(lse2 - mx);
+        const float den = e1 + e2;
+        w_prev = e1 / den;
+        inv *= e2 / den;
+        lse2 = mx + log2f(den);
+      }
+    }
+    if (row_ok) p.lse[batch * p.ls[0] + head * p.ls[1] + row] = p.lse_natural ? lse2 * 0.6931471805599453f : lse2;
+    const int64_t o_off = batch * p.os[0] + static_cast<int64_t>(row) * p.os[1] + head * p.os[2];
+    const int64_t po_off = batch * p.pos[0] + static_cast<int64_t>(row) * p.pos[1] + head * p.pos[2];
+#pragma unroll
+    for (int cchunk = 0; cchunk < kDV / 32; ++cchunk) {
+      uint32_t orr[32];
+      if (nb > 0) {
+        tmem_ld32(tO + cchunk * 32, orr);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) orr[i] = 0u;
+      }
+      if (dump) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) p.dbg[2 * 16384 + row_in_tile * 128 + cchunk * 32 + i] = __uint_as_float(orr[i]);
+      }
+      if (row_ok) {
+        float ov[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ov[i] = __uint_as_float(orr[i]) * inv;
+        if (p.prev_o != nullptr) {
+          const float4* pp = reinterpret_cast<const float4*>(p.prev_o + po_off + cchunk * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 x = pp[i];
+            ov[4 * i] = fmaf(w_prev, x.x, ov[4 * i]);
+            ov[4 * i + 1] = fmaf(w_prev, x.y, ov[4 * i + 1]);
+            ov[4 * i + 2] = fmaf(w_prev, x.z, ov[4 * i + 2]);
+            ov[4 * i + 3] = fmaf(w_prev, x.w, ov[4 * i + 3]);
+          }
+        }
+        if (p.o_fp32) {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + o_off + cchunk * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[i] = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.o) + o_off + cchunk * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = make_uint4(pack_bf16(ov[8 * i], ov[8 * i + 1]), pack_bf16(ov[8 * i + 2], ov[8 * i + 3]),
+                                pack_bf16(ov[8 * i + 4], ov[8 * i + 5]), pack_bf16(ov[8 * i + 6], ov[8 * i + 7]));
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    // Something gave up waiting: let copies and MMAs still in flight drain before the
+    // shared memory and TMEM of this CTA are handed back.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DQK, int BN, int KST, int VST>
+static int launch_fwd(const pith_attn_fwd_args* a, const FwdParams& p, cudaStream_t st) {
+  using L = FwdSmem<DQK, BN, KST, VST>;
+  CUtensorMap tq, tk, tv;
+  if (int rc = make_tensor_map(&tq, a->q, 2, a->B, a->Sq, a->Hq, a->Dqk, a->q_stride, 64, kBM)) return rc;
+  if (int rc = make_tensor_map(&tk, a->k, 2, a->B, a->Sk, a->Hkv, a->Dqk, a->k_stride, 64, BN)) return rc;
+  if (int rc = make_tensor_map(&tv, a->v, 2, a->B, a->Sk, a->Hkv, a->Dv, a->v_stride, 64, BN)) return rc;
+  auto kern = attn_fwd_kernel<DQK, BN, KST, VST>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    PITH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
+    attr_set = true;
+  }
+  dim3 grid((a->Sq + 2 * kBM - 1) / (2 * kBM), a->Hq, a->B);
+  kern<<<grid, kFwdThreads, L::kAlloc, st>>>(tq, tk, tv, p);
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace pith
+
+using namespace pith;
+
+extern "C" int pith_attn_fwd(const pith_attn_fwd_args* a, void* stream) {
+  PITH_REQUIRE(a != nullptr, "null args");
+  PITH_REQUIRE(a->q && a->k && a->v && a->o && a->lse, "null tensor pointer");
+  PITH_REQUIRE(a->B > 0 && a->Sq > 0 && a->Sk > 0 && a->Hq > 0 && a->Hkv > 0, "bad shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d",
+               a->B, a->Sq, a->Sk, a->Hq, a->Hkv);
+  PITH_REQUIRE(a->Hq % a->Hkv == 0, "Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
+  PITH_REQUIRE(a->Dv == 128 && (a->Dqk == 128 || a->Dqk == 192),
+               "unsupported head dims Dqk=%d Dv=%d (supported: 128/128 and 192/128)", a->Dqk, a->Dv);
+  PITH_REQUIRE((a->prev_o == nullptr) == (a->prev_lse == nullptr), "prev_o and prev_lse must be given together");
+  PITH_REQUIRE(a->softmax_scale > 0.f, "softmax_scale must be positive");
+  PITH_REQUIRE(a->Hq <= 65535 && a->B <= 65535, "Hq and B must fit a grid dimension");
+  const bool o32 = (a->flags & PITH_FWD_O_FP32) != 0;
+  const int oeb = o32 ? 4 : 2;
+  PITH_REQUIRE(aligned16(a->o) && (a->o_stride[0] * oeb) % 16 == 0 && (a->o_stride[1] * oeb) % 16 == 0 &&
+                   (a->o_stride[2] * oeb) % 16 == 0,
+               "o must be 16-byte aligned with 16-byte-multiple strides");
+  if (a->prev_o)
+    PITH_REQUIRE(aligned16(a->prev_o) && a->prev_o_stride[0] % 4 == 0 && a->prev_o_stride[1] % 4 == 0 &&
+                     a->prev_o_stride[2] % 4 == 0,
+                 "prev_o must be 16-byte aligned with 16-byte-multiple strides");
+  if (int rc = require_sm100()) return rc;
+  FwdParams p;
+  p.o = a->o; p.lse = a->lse; p.prev_o = a->prev_o; p.prev_lse = a->prev_lse; p.dbg = a->debug; p.status = a->status;
+  p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
+  p.causal = a->causal ? 1 : 0; p.causal_off = a->causal_offset;
+  p.o_fp32 = o32 ? 1 : 0; p.lse_natural = (a->flags & PITH_FWD_LSE_NATURAL) ? 1 : 0;
+  p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  for (int i = 0; i < 3; ++i) { p.os[i] = a->o_stride[i]; p.pos[i] = a->prev_o ? a->prev_o_stride[i] : 0; }
+  for (int i = 0; i < 2; ++i) { p.ls[i] = a->lse_stride[i]; p.pls[i] = a->prev_lse ? a->prev_lse_stride[i] : 0; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->Dqk == 128) return launch_fwd<128, 128, 2, 2>(a, p, st);
+  return launch_fwd<192, 128, 2, 1>(a, p, st);
+}

@@ -1,0 +1,251 @@
+// HBM-bound kernels of the ring-attention path: the online-softmax merge of two partial
+// results, delta = rowsum(O * dO), and the final fp32 -> bf16 rounding of an accumulator.
+// Each thread moves 8 consecutive elements of one [b][s][h] row with 16-byte accesses;
+// consecutive threads walk the row, consecutive rows walk s, so both the row data and the
+// [B][H][S] statistics are read and written in whole sectors.
+#include "../../include/pith_b200.h"
+#include "common.cuh"
+#include "host_common.h"
+
+namespace pith {
+
+struct Vec8 {
+  float v[8];
+};
+
+template <bool F32>
+__device__ __forceinline__ Vec8 load8(const void* base, int64_t elem_off) {
+  Vec8 r;
+  if constexpr (F32) {
+    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + elem_off);
+    float4 a = __ldg(p), b = __ldg(p + 1);
+    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w;
+    r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+  } else {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + elem_off));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r.v[2 * i] = __uint_as_float(w[i] << 16);
+      r.v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  return r;
+}
+
+struct RowIndex {
+  int b, s, h, chunk;
+};
+
+__device__ __forceinline__ RowIndex decode_item(int64_t item, int chunks, int S, int H) {
+  RowIndex r;
+  r.chunk = static_cast<int>(item % chunks);
+  int64_t row = item / chunks;
+  r.s = static_cast<int>(row % S);
+  row /= S;
+  r.h = static_cast<int>(row % H);
+  r.b = static_cast<int>(row / H);
+  return r;
+}
+
+struct CombineParams {
+  const void* out1;
+  const void* out2;
+  const float* lse1;
+  const float* lse2;
+  float* out;
+  float* lse;
+  int B, S, H, D;
+  int64_t o1s[3], o2s[3];
+  int64_t l1s[2], l2s[2];
+};
+
+template <bool F32A, bool F32B, bool NATURAL>
+__global__ void __launch_bounds__(256) combine_kernel(const CombineParams p) {
+  const int chunks = p.D >> 3;
+  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.S * chunks;
+  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < total;
+       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const RowIndex r = decode_item(item, chunks, p.S, p.H);
+    const float l1 = __ldg(p.lse1 + r.b * p.l1s[0] + r.h * p.l1s[1] + r.s);
+    const float l2 = __ldg(p.lse2 + r.b * p.l2s[0] + r.h * p.l2s[1] + r.s);
+    const float mx = fmaxf(l1, l2);
+    float e1, e2, lse;
+    if constexpr (NATURAL) {
+      e1 = expf(l1 - mx);
+      e2 = expf(l2 - mx);
+      lse = mx + logf(e1 + e2);
+    } else {
+      e1 = exp2f(l1 - mx);
+      e2 = exp2f(l2 - mx);
+      lse = mx + log2f(e1 + e2);
+    }
+    const float den = e1 + e2;
+    const int d0 = r.chunk << 3;
+    const Vec8 a = load8<F32A>(p.out1, r.b * p.o1s[0] + r.s * p.o1s[1] + r.h * p.o1s[2] + d0);
+    const Vec8 c = load8<F32B>(p.out2, r.b * p.o2s[0] + r.s * p.o2s[1] + r.h * p.o2s[2] + d0);
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = (e1 * a.v[i] + e2 * c.v[i]) / den;
+    float4* dst = reinterpret_cast<float4*>(p.out + ((static_cast<int64_t>(r.b) * p.S + r.s) * p.H + r.h) * p.D + d0);
+    dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+    if (r.chunk == 0) p.lse[(static_cast<int64_t>(r.b) * p.H + r.h) * p.S + r.s] = lse;
+  }
+}
+
+struct DeltaParams {
+  const void* o;
+  const void* dout;
+  float* delta;
+  int B, S, H, D;
+  int64_t os[3], dos[3];
+  int64_t ds[2];
+};
+
+// One 16-lane group per row when D = 128; the partial dot products are folded with shuffles.
+__global__ void __launch_bounds__(256) delta_kernel(const DeltaParams p) {
+  const int chunks = p.D >> 3;  // power of two <= 32 (checked on the host)
+  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.S * chunks;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t rounds = (total + stride - 1) / stride;
+  int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  for (int64_t it = 0; it < rounds; ++it, item += stride) {
+    float acc = 0.f;
+    RowIndex r = {0, 0, 0, 0};
+    const bool live = item < total;
+    if (live) {
+      r = decode_item(item, chunks, p.S, p.H);
+      const int d0 = r.chunk << 3;
+      const Vec8 a = load8<false>(p.o, r.b * p.os[0] + r.s * p.os[1] + r.h * p.os[2] + d0);
+      const Vec8 c = load8<false>(p.dout, r.b * p.dos[0] + r.s * p.dos[1] + r.h * p.dos[2] + d0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fmaf(a.v[i], c.v[i], acc);
+    }
+    for (int off = chunks >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    if (live && r.chunk == 0) p.delta[r.b * p.ds[0] + r.h * p.ds[1] + r.s] = acc;
+  }
+}
+
+struct CastParams {
+  const float* acc;
+  __nv_bfloat16* out;
+  int B, S, H, D;
+  int64_t as[3], os[3];
+  float scale;
+};
+
+__global__ void __launch_bounds__(256) cast_kernel(const CastParams p) {
+  const int chunks = p.D >> 3;
+  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.S * chunks;
+  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < total;
+       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    // rows ordered (b, s, h) here: both tensors are walked in their storage order
+    const int chunk = static_cast<int>(item % chunks);
+    int64_t row = item / chunks;
+    const int h = static_cast<int>(row % p.H);
+    row /= p.H;
+    const int s = static_cast<int>(row % p.S);
+    const int b = static_cast<int>(row / p.S);
+    const int d0 = chunk << 3;
+    const Vec8 a = load8<true>(p.acc, b * p.as[0] + s * p.as[1] + h * p.as[2] + d0);
+    uint4 u;
+    u.x = pack_bf16(a.v[0] * p.scale, a.v[1] * p.scale);
+    u.y = pack_bf16(a.v[2] * p.scale, a.v[3] * p.scale);
+    u.z = pack_bf16(a.v[4] * p.scale, a.v[5] * p.scale);
+    u.w = pack_bf16(a.v[6] * p.scale, a.v[7] * p.scale);
+    *reinterpret_cast<uint4*>(p.out + b * p.os[0] + s * p.os[1] + h * p.os[2] + d0) = u;
+  }
+}
+
+static int grid_for(int64_t total_items) {
+  // 148 SMs x 8 resident 256-thread blocks; fewer when the problem is smaller.
+  int64_t blocks = (total_items + 255) / 256;
+  const int64_t cap = 148 * 8;
+  return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+static bool rows_ok(const void* base, const int64_t st[3], int elem_bytes) {
+  return aligned16(base) && (st[0] * elem_bytes) % 16 == 0 && (st[1] * elem_bytes) % 16 == 0 &&
+         (st[2] * elem_bytes) % 16 == 0;
+}
+
+}  // namespace pith
+
+using namespace pith;
+
+extern "C" int pith_combine(const pith_combine_args* a, void* stream) {
+  PITH_REQUIRE(a != nullptr, "null args");
+  PITH_REQUIRE(a->out1 && a->out2 && a->lse1 && a->lse2 && a->out && a->lse, "null tensor pointer");
+  PITH_REQUIRE(a->B >= 0 && a->S >= 0 && a->H >= 0 && a->D > 0 && a->D % 8 == 0, "bad shape %dx%dx%dx%d", a->B, a->S,
+               a->H, a->D);
+  PITH_REQUIRE((a->out1_dtype | 1) == 1 && (a->out2_dtype | 1) == 1, "unknown dtype");
+  PITH_REQUIRE(rows_ok(a->out1, a->out1_stride, a->out1_dtype == PITH_DTYPE_F32 ? 4 : 2) &&
+                   rows_ok(a->out2, a->out2_stride, a->out2_dtype == PITH_DTYPE_F32 ? 4 : 2) && aligned16(a->out),
+               "out tensors must be 16-byte aligned with 16-byte-multiple strides");
+  if (static_cast<int64_t>(a->B) * a->S * a->H == 0) return kOk;
+  if (int rc = require_sm100()) return rc;
+  CombineParams p;
+  p.out1 = a->out1; p.out2 = a->out2; p.lse1 = a->lse1; p.lse2 = a->lse2; p.out = a->out; p.lse = a->lse;
+  p.B = a->B; p.S = a->S; p.H = a->H; p.D = a->D;
+  for (int i = 0; i < 3; ++i) { p.o1s[i] = a->out1_stride[i]; p.o2s[i] = a->out2_stride[i]; }
+  for (int i = 0; i < 2; ++i) { p.l1s[i] = a->lse1_stride[i]; p.l2s[i] = a->lse2_stride[i]; }
+  const int64_t items = static_cast<int64_t>(a->B) * a->S * a->H * (a->D / 8);
+  const int grid = grid_for(items);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool nat = (a->flags & PITH_COMBINE_NATURAL) != 0;
+  const int sel = (a->out1_dtype == PITH_DTYPE_F32 ? 4 : 0) | (a->out2_dtype == PITH_DTYPE_F32 ? 2 : 0) | (nat ? 1 : 0);
+  switch (sel) {
+    case 0: combine_kernel<false, false, false><<<grid, 256, 0, st>>>(p); break;
+    case 1: combine_kernel<false, false, true><<<grid, 256, 0, st>>>(p); break;
+    case 2: combine_kernel<false, true, false><<<grid, 256, 0, st>>>(p); break;
+    case 3: combine_kernel<false, true, true><<<grid, 256, 0, st>>>(p); break;
+    case 4: combine_kernel<true, false, false><<<grid, 256, 0, st>>>(p); break;
+    case 5: combine_kernel<true, false, true><<<grid, 256, 0, st>>>(p); break;
+    case 6: combine_kernel<true, true, false><<<grid, 256, 0, st>>>(p); break;
+    default: combine_kernel<true, true, true><<<grid, 256, 0, st>>>(p); break;
+  }
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+extern "C" int pith_attn_bwd_preprocess(const pith_bwd_preprocess_args* a, void* stream) {
+  PITH_REQUIRE(a != nullptr, "null args");
+  PITH_REQUIRE(a->o && a->dout && a->delta, "null tensor pointer");
+  const int chunks = a->Dv / 8;
+  PITH_REQUIRE(a->Dv > 0 && a->Dv % 8 == 0 && chunks <= 32 && (chunks & (chunks - 1)) == 0,
+               "Dv = %d must be 8 * a power of two, at most 256", a->Dv);
+  PITH_REQUIRE(a->B >= 0 && a->S >= 0 && a->H >= 0, "bad shape");
+  PITH_REQUIRE(rows_ok(a->o, a->o_stride, 2) && rows_ok(a->dout, a->do_stride, 2),
+               "o / dout must be 16-byte aligned with 16-byte-multiple strides");
+  if (static_cast<int64_t>(a->B) * a->S * a->H == 0) return kOk;
+  if (int rc = require_sm100()) return rc;
+  DeltaParams p;
+  p.o = a->o; p.dout = a->dout; p.delta = a->delta;
+  p.B = a->B; p.S = a->S; p.H = a->H; p.D = a->Dv;
+  for (int i = 0; i < 3; ++i) { p.os[i] = a->o_stride[i]; p.dos[i] = a->do_stride[i]; }
+  p.ds[0] = a->delta_stride[0]; p.ds[1] = a->delta_stride[1];
+  const int64_t items = static_cast<int64_t>(a->B) * a->S * a->H * chunks;
+  delta_kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+extern "C" int pith_cast_f32_to_bf16(const float* acc, void* out, int32_t B, int32_t S, int32_t H, int32_t D,
+                                     const int64_t acc_stride[3], const int64_t out_stride[3], float scale,
+                                     void* stream) {
+  PITH_REQUIRE(acc && out && acc_stride && out_stride, "null pointer");
+  PITH_REQUIRE(B >= 0 && S >= 0 && H >= 0 && D > 0 && D % 8 == 0, "bad shape %dx%dx%dx%d", B, S, H, D);
+  PITH_REQUIRE(rows_ok(acc, acc_stride, 4) && rows_ok(out, out_stride, 2),
+               "tensors must be 16-byte aligned with 16-byte-multiple strides");
+  if (static_cast<int64_t>(B) * S * H == 0) return kOk;
+  if (int rc = require_sm100()) return rc;
+  CastParams p;
+  p.acc = acc; p.out = static_cast<__nv_bfloat16*>(out);
+  p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
+  for (int i = 0; i < 3; ++i) { p.as[i] = acc_stride[i]; p.os[i] = out_stride[i]; }
+  const int64_t items = static_cast<int64_t>(B) * S * H * (D / 8);
+  cast_kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}

@@ -1,0 +1,166 @@
+"""Thin tensor-level wrappers over the C ABI: pointer / stride marshalling and nothing else.
+
+All functions enqueue on the current CUDA stream of the tensors' device and return immediately.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import I64x2, I64x3
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device uint32 the kernels write to when a bounded wait gives up (0 = healthy)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w
+
+
+def check_device_status(device=None) -> None:
+    """Synchronises and raises if any kernel launched so far reported a device-side anomaly."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = status_word(device)
+    val = int(w.item()) & 0xFFFFFFFF
+    if val != 0:
+        w.zero_()
+        text = _lib.load().pith_status_string(val).decode()
+        raise RuntimeError(f"pith_b200 kernel reported: {text}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _bshd(t: torch.Tensor, name: str) -> I64x3:
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise ValueError(f"{name} must be [B,S,H,D] with a contiguous last dimension, got {tuple(t.shape)} "
+                         f"strides {t.stride()}")
+    return I64x3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _bhs(t: torch.Tensor, name: str) -> I64x2:
+    if t.dim() != 3 or t.stride(2) != 1 or t.dtype != torch.float32:
+        raise ValueError(f"{name} must be fp32 [B,H,S] with unit stride along S")
+    return I64x2(t.stride(0), t.stride(1))
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("pith_b200 operators run on CUDA tensors only (no CPU fallback)")
+
+
+def attn_fwd(q, k, v, softmax_scale: float, causal: bool, causal_offset: int = 0, *, out=None, lse=None,
+             prev_o=None, prev_lse=None, out_fp32: bool = False, lse_natural: bool = False, debug=None):
+    """One attention block: returns (O [B,Sq,Hq,Dv], LSE [B,Hq,Sq]); see ``pith_attn_fwd``."""
+    _require_cuda(q, k, v, out, lse, prev_o, prev_lse)
+    B, Sq, Hq, Dqk = q.shape
+    _, Sk, Hkv, Dv = v.shape
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise TypeError("q, k, v must be bfloat16")
+    if out is None:
+        out = torch.empty((B, Sq, Hq, Dv), dtype=torch.float32 if out_fp32 else torch.bfloat16, device=q.device)
+    else:
+        out_fp32 = out.dtype == torch.float32
+    if lse is None:
+        lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
+    a = _lib.AttnFwdArgs()
+    a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.prev_o = prev_o.data_ptr() if prev_o is not None else None
+    a.prev_lse = prev_lse.data_ptr() if prev_lse is not None else None
+    a.debug = debug.data_ptr() if debug is not None else None
+    a.status = status_word(q.device).data_ptr()
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
+    a.causal, a.causal_offset = int(bool(causal)), int(causal_offset)
+    a.flags = (_lib.FWD_O_FP32 if out_fp32 else 0) | (_lib.FWD_LSE_NATURAL if lse_natural else 0)
+    a.softmax_scale = float(softmax_scale)
+    a.q_stride, a.k_stride, a.v_stride = _bshd(q, "q"), _bshd(k, "k"), _bshd(v, "v")
+    a.o_stride = _bshd(out, "out")
+    a.lse_stride = _bhs(lse, "lse")
+    if prev_o is not None:
+        if prev_o.dtype != torch.float32:
+            raise TypeError("prev_o must be float32")
+        a.prev_o_stride = _bshd(prev_o, "prev_o")
+        a.prev_lse_stride = _bhs(prev_lse, "prev_lse")
+    _lib.check(_lib.load().pith_attn_fwd(ctypes.byref(a), _stream(q)), "pith_attn_fwd")
+    return out, lse
+
+
+def bwd_preprocess(o, dout, delta=None):
+    """delta [B,H,S] = rowsum(o * dout); see ``pith_attn_bwd_preprocess``."""
+    _require_cuda(o, dout, delta)
+    B, S, H, Dv = o.shape
+    if delta is None:
+        delta = torch.empty((B, H, S), dtype=torch.float32, device=o.device)
+    a = _lib.BwdPreprocessArgs()
+    a.o, a.dout, a.delta = o.data_ptr(), dout.data_ptr(), delta.data_ptr()
+    a.B, a.S, a.H, a.Dv = B, S, H, Dv
+    a.o_stride, a.do_stride, a.delta_stride = _bshd(o, "o"), _bshd(dout, "dout"), _bhs(delta, "delta")
+    _lib.check(_lib.load().pith_attn_bwd_preprocess(ctypes.byref(a), _stream(o)), "pith_attn_bwd_preprocess")
+    return delta
+
+
+def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool, causal_offset: int,
+             dq_acc, dk_acc, dv_acc, debug=None):
+    """Adds this block's dQ/dK/dV into the fp32 accumulators; see ``pith_attn_bwd``."""
+    _require_cuda(q, k, v, dout, lse_log2, delta, dq_acc, dk_acc, dv_acc)
+    B, Sq, Hq, Dqk = q.shape
+    _, Sk, Hkv, Dv = v.shape
+    for t, n in ((dq_acc, "dq_acc"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
+        if t.dtype != torch.float32:
+            raise TypeError(f"{n} must be float32")
+    a = _lib.AttnBwdArgs()
+    a.q, a.k, a.v, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
+    a.lse, a.delta = lse_log2.data_ptr(), delta.data_ptr()
+    a.dq_acc, a.dk_acc, a.dv_acc = dq_acc.data_ptr(), dk_acc.data_ptr(), dv_acc.data_ptr()
+    a.status = status_word(q.device).data_ptr()
+    a.debug = debug.data_ptr() if debug is not None else None
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
+    a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), 0
+    a.softmax_scale = float(softmax_scale)
+    a.q_stride, a.k_stride, a.v_stride, a.do_stride = _bshd(q, "q"), _bshd(k, "k"), _bshd(v, "v"), _bshd(dout, "dout")
+    a.dq_stride, a.dk_stride, a.dv_stride = _bshd(dq_acc, "dq_acc"), _bshd(dk_acc, "dk_acc"), _bshd(dv_acc, "dv_acc")
+    a.lse_stride, a.delta_stride = _bhs(lse_log2, "lse"), _bhs(delta, "delta")
+    _lib.check(_lib.load().pith_attn_bwd(ctypes.byref(a), _stream(q)), "pith_attn_bwd")
+
+
+def cast_to_bf16(acc, out=None, scale: float = 1.0):
+    """bf16(acc * scale) for an fp32 [B,S,H,D] accumulator; see ``pith_cast_f32_to_bf16``."""
+    _require_cuda(acc, out)
+    B, S, H, D = acc.shape
+    if out is None:
+        out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=acc.device)
+    _lib.check(_lib.load().pith_cast_f32_to_bf16(acc.data_ptr(), out.data_ptr(), B, S, H, D, _bshd(acc, "acc"),
+                                                 _bshd(out, "out"), float(scale), _stream(acc)),
+               "pith_cast_f32_to_bf16")
+    return out
+
+
+def combine(out1, lse1, out2, lse2, natural: bool):
+    """Online-softmax merge; returns (fp32 out [B,S,H,D], fp32 lse [B,H,S]); see ``pith_combine``."""
+    _require_cuda(out1, lse1, out2, lse2)
+    B, S, H, D = out1.shape
+    dt = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+    if out1.dtype not in dt or out2.dtype not in dt:
+        raise TypeError("combine inputs must be bfloat16 or float32")
+    out = torch.empty((B, S, H, D), dtype=torch.float32, device=out1.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=out1.device)
+    a = _lib.CombineArgs()
+    a.out1, a.lse1, a.out2, a.lse2 = out1.data_ptr(), lse1.data_ptr(), out2.data_ptr(), lse2.data_ptr()
+    a.out, a.lse = out.data_ptr(), lse.data_ptr()
+    a.out1_dtype, a.out2_dtype = dt[out1.dtype], dt[out2.dtype]
+    a.B, a.S, a.H, a.D = B, S, H, D
+    a.flags = _lib.COMBINE_NATURAL if natural else 0
+    a.out1_stride, a.out2_stride = _bshd(out1, "out1"), _bshd(out2, "out2")
+    a.lse1_stride, a.lse2_stride = _bhs(lse1, "lse1"), _bhs(lse2, "lse2")
+    _lib.check(_lib.load().pith_combine(ctypes.byref(a), _stream(out1)), "pith_combine")
+    return out, lse
