@@ -1,7 +1,469 @@
-// placeholder until the backward kernel lands
+// Attention backward for sm_100a. One kernel template, two modes, both built from the same
+// pipeline: a 128-row tile stays resident in shared memory, 64-row tiles stream past it through
+// a TMA ring, tcgen05 MMAs produce two [128 x 64] fp32 tiles in TMEM, two warpgroups turn them
+// into bf16 operands (written back into TMEM) and a second round of MMAs accumulates the result.
+//
+//   mode kDkDv: resident K_n, V_n (128 keys); streamed Q_i, dO_i (64 queries)
+//       T1 = K Q_i^T (= S^T)      T2 = V dO_i^T (= dP^T)          lane = key, column = query
+//       A1 = P^T = exp2(T1 c - lse)     A2 = dS^T = P^T (T2 - delta)
+//       dV += A1 dO_i             dK += A2 Q_i
+//   mode kDq:   resident Q_m, dO_m (128 queries); streamed K_j, V_j (64 keys)
+//       T1 = Q K_j^T (= S)        T2 = dO V_j^T (= dP)            lane = query, column = key
+//       A2 = dS = exp2(T1 c - lse) (T2 - delta)
+//       dQ += A2 K_j
+// lse is the log2-domain LSE of the COMPLETE softmax row and delta = rowsum(O dO), so one
+// (Q block, KV block) pair of a ring step yields exactly its share of the gradients.
+// Results are scaled (dK, dQ by softmax_scale) and added to fp32 accumulators with vector
+// atomics, so ring steps and the query heads of a GQA group round to bf16 only once.
+//
+// Warp roles (384 threads): warp 0 TMA producer (+ the per-query statistics of the streamed tile
+// in mode kDkDv), warp 1 MMA issuer, warps 4..7 / 8..11 two compute groups that alternate
+// iterations (and TMEM buffers when two fit), so the tensor core works on one iteration while
+// the other is in the exponentials.
+//
+// TMEM columns: buffer b at [128 b, 128 b + 128): T1 in the first 64 columns, T2 in the last 64;
+// A1 / A2 (packed bf16) overlay the first 32 columns of T1 / T2. Accumulators follow the buffers.
 #include "../../include/pith_b200.h"
+#include "common.cuh"
 #include "host_common.h"
+
+namespace pith {
+
+enum BwdMode : int { kDkDv = 0, kDq = 1 };
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  float* dq_acc;
+  float* dk_acc;
+  float* dv_acc;
+  float* dbg;
+  uint32_t* status;
+  int B, Sq, Sk, Hq, Hkv;
+  int causal, causal_off;
+  float scale_log2, scale;
+  int64_t dqs[3], dks[3], dvs[3];
+  int64_t ls[2], dls[2];
+};
+
+constexpr int kBwdThreads = 384;
+constexpr int kRes = 128;  // rows of the resident tile (= TMEM lanes)
+constexpr int kStr = 64;   // rows of a streamed tile (= columns of T1 / T2)
+
+template <int DQK, int MODE>
+struct BwdCfg {
+  static constexpr int NBUF = (MODE == kDkDv && DQK == 192) ? 1 : 2;
+  static constexpr int NST = (DQK == 128) ? 4 : 3;
+  static constexpr int kR1 = kRes * DQK * 2;
+  static constexpr int kR2 = kRes * 128 * 2;
+  static constexpr int kX1 = kStr * DQK * 2;
+  static constexpr int kX2 = kStr * 128 * 2;
+  static constexpr int kR1Off = 0;
+  static constexpr int kR2Off = kR1Off + kR1;
+  static constexpr int kX1Off = kR2Off + kR2;
+  static constexpr int kX2Off = kX1Off + NST * kX1;
+  static constexpr int kStatOff = kX2Off + NST * kX2;        // [NST][2][64] floats
+  static constexpr int kBarOff = kStatOff + NST * 2 * kStr * 4;
+  static constexpr int kNumBars = 1 + 2 * NST + 2 + 2 + 1;
+  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+  static constexpr int kAlloc = kTotal + 1024;
+  static constexpr int kAccCol = NBUF * 128;  // first accumulator column
+};
+
+template <int DQK, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
+                    const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
+                    const BwdParams p) {
+  using C = BwdCfg<DQK, MODE>;
+  constexpr int NBUF = C::NBUF, NST = C::NST;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sR1 = smem + C::kR1Off;
+  uint8_t* sR2 = smem + C::kR2Off;
+  uint8_t* sX1 = smem + C::kX1Off;
+  uint8_t* sX2 = smem + C::kX2Off;
+  float* sStat = reinterpret_cast<float*>(smem + C::kStatOff);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
+  uint64_t* res_full = bars;
+  uint64_t* x_full = bars + 1;
+  uint64_t* x_empty = x_full + NST;
+  uint64_t* t_full = x_empty + NST;  // [2], by compute group
+  uint64_t* a_full = t_full + 2;     // [2]
+  uint64_t* acc_full = a_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const AbortCtl ctl{p.status, abort_flag};
+
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.Hq / p.Hkv);
+  // Tile of the resident operand and the range of streamed tiles it meets.
+  int r0, it_begin, it_end;
+  if constexpr (MODE == kDkDv) {
+    r0 = blockIdx.x * kRes;  // first key; small r0 = most work, launched first
+    it_begin = p.causal ? max(0, r0 - p.causal_off) / kStr : 0;
+    it_end = (p.Sq + kStr - 1) / kStr;
+  } else {
+    r0 = (gridDim.x - 1 - blockIdx.x) * kRes;  // first query; late queries first
+    it_begin = 0;
+    it_end = (p.Sk + kStr - 1) / kStr;
+    if (p.causal) {
+      const int last_key = min(r0 + kRes - 1, p.Sq - 1) + p.causal_off;
+      it_end = last_key < 0 ? 0 : min(it_end, last_key / kStr + 1);
+    }
+  }
+  const int n_it = max(0, it_end - it_begin);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0u;
+    mbar_init(res_full, 1);
+    for (int i = 0; i < NST; ++i) {
+      mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
+      mbar_init(&x_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&a_full[i], 128);
+    }
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int r1_head = (MODE == kDkDv) ? kv_head : head;  // head index of the resident tensors
+  const int x_head = (MODE == kDkDv) ? head : kv_head;   // head index of the streamed tensors
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (n_it > 0) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tm_r1);
+        tma_prefetch_desc(&tm_r2);
+        tma_prefetch_desc(&tm_x1);
+        tma_prefetch_desc(&tm_x2);
+        mbar_arrive_expect_tx(res_full, C::kR1 + C::kR2);
+#pragma unroll
+        for (int sub = 0; sub < DQK / 64; ++sub)
+          tma_load_4d(sR1 + sub * (kRes * 128), &tm_r1, res_full, sub * 64, r1_head, r0, batch);
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub)
+          tma_load_4d(sR2 + sub * (kRes * 128), &tm_r2, res_full, sub * 64, r1_head, r0, batch);
+      }
+      for (int k = 0; k < n_it; ++k) {
+        const int s = k % NST;
+        const int x0 = (it_begin + k) * kStr;
+        if (lane == 0) mbar_wait(&x_empty[s], ((k / NST) & 1) ^ 1, ctl, 0x100 + s);
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&x_full[s], C::kX1 + C::kX2);
+#pragma unroll
+          for (int sub = 0; sub < DQK / 64; ++sub)
+            tma_load_4d(sX1 + s * C::kX1 + sub * (kStr * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub)
+            tma_load_4d(sX2 + s * C::kX2 + sub * (kStr * 128), &tm_x2, &x_full[s], sub * 64, x_head, x0, batch);
+        }
+        if constexpr (MODE == kDkDv) {
+          // statistics of the 64 streamed queries: lse (+inf where the row does not exist or saw no key), delta
+#pragma unroll
+          for (int r = lane; r < kStr; r += 32) {
+            const int m = x0 + r;
+            float l = INFINITY, d = 0.f;
+            if (m < p.Sq) {
+              l = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
+              d = p.delta[batch * p.dls[0] + head * p.dls[1] + m];
+              if (l == -INFINITY) l = INFINITY;
+            }
+            sStat[(s * 2 + 0) * kStr + r] = l;
+            sStat[(s * 2 + 1) * kStr + r] = d;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&x_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_t = make_idesc_bf16(kRes, kStr, false, false);
+      constexpr uint32_t idesc_dv = make_idesc_bf16(kRes, 128, false, true);
+      constexpr uint32_t idesc_dqk = make_idesc_bf16(kRes, DQK, false, true);
+      const uint32_t r1 = smem_u32(sR1), r2 = smem_u32(sR2), x1 = smem_u32(sX1), x2 = smem_u32(sX2);
+      mbar_wait(res_full, 0, ctl, 0x200);
+      auto issue_t = [&](int k) {
+        const int s = k % NST, b = k % NBUF;
+        mbar_wait(&x_full[s], (k / NST) & 1, ctl, 0x300 + s);
+        tc_fence_after_sync();
+        const uint32_t t1 = tmem_base + b * 128, t2 = t1 + 64;
+#pragma unroll
+        for (int kk = 0; kk < DQK / 16; ++kk) {
+          const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
+          umma_ss(t1, make_smem_desc(r1 + sub * (kRes * 128) + off, 16, 1024),
+                  make_smem_desc(x1 + s * C::kX1 + sub * (kStr * 128) + off, 16, 1024), idesc_t, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
+          umma_ss(t2, make_smem_desc(r2 + sub * (kRes * 128) + off, 16, 1024),
+                  make_smem_desc(x2 + s * C::kX2 + sub * (kStr * 128) + off, 16, 1024), idesc_t, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&t_full[k & 1]);
+      };
+      issue_t(0);
+      for (int k = 0; k < n_it; ++k) {
+        if (NBUF == 2 && k + 1 < n_it) issue_t(k + 1);
+        const int s = k % NST, b = k % NBUF;
+        mbar_wait(&a_full[k & 1], (k >> 1) & 1, ctl, 0x400 + (k & 1));
+        tc_fence_after_sync();
+        const uint32_t a1 = tmem_base + b * 128, a2 = a1 + 64;
+        const uint32_t acc = k > 0 ? 1u : 0u;
+        if constexpr (MODE == kDkDv) {
+#pragma unroll
+          for (int kk = 0; kk < kStr / 16; ++kk)  // dV += P^T dO_i
+            umma_ts(tmem_base + C::kAccCol, a1 + kk * 8,
+                    make_smem_desc(x2 + s * C::kX2 + kk * 2048, kStr * 128, 1024), idesc_dv, acc | (kk > 0 ? 1u : 0u));
+#pragma unroll
+          for (int kk = 0; kk < kStr / 16; ++kk)  // dK += dS^T Q_i
+            umma_ts(tmem_base + C::kAccCol + 128, a2 + kk * 8,
+                    make_smem_desc(x1 + s * C::kX1 + kk * 2048, kStr * 128, 1024), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kStr / 16; ++kk)  // dQ += dS K_j
+            umma_ts(tmem_base + C::kAccCol, a2 + kk * 8,
+                    make_smem_desc(x1 + s * C::kX1 + kk * 2048, kStr * 128, 1024), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
+        }
+        umma_commit(&x_empty[s]);
+        if (NBUF == 1 && k + 1 < n_it) issue_t(k + 1);
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ compute groups
+    const int w = (warp - 4) >> 2;
+    const int lane_row = ((warp & 3) << 5) + lane;  // TMEM lane = row of the resident tile
+    const int res_row = r0 + lane_row;              // key (kDkDv) or query (kDq) position
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
+    const float c = p.scale_log2;
+    float my_lse = INFINITY, my_delta = 0.f;
+    if constexpr (MODE == kDq) {
+      if (res_row < p.Sq && n_it > 0) {
+        my_lse = p.lse[batch * p.ls[0] + head * p.ls[1] + res_row];
+        my_delta = p.delta[batch * p.dls[0] + head * p.dls[1] + res_row];
+        if (my_lse == -INFINITY) my_lse = INFINITY;
+      }
+    }
+    for (int k = w; k < n_it; k += 2) {
+      const int s = k % NST, b = k % NBUF;
+      const int x0 = (it_begin + k) * kStr;
+      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k / NST) & 1, ctl, 0x500 + s);
+      mbar_wait(&t_full[w], (k >> 1) & 1, ctl, 0x600 + w);
+      tc_fence_after_sync();
+      const uint32_t t1 = tmem_base + lane_addr + b * 128, t2 = t1 + 64;
+      uint32_t s1[kStr], s2[kStr];
+      tmem_ld32(t1, s1);
+      tmem_ld32(t1 + 32, s1 + 32);
+      tmem_ld32(t2, s2);
+      tmem_ld32(t2 + 32, s2 + 32);
+      tmem_wait_ld();
+      if (p.dbg != nullptr && blockIdx.x == 0 && head == 0 && batch == 0 && k == 0) {
+#pragma unroll
+        for (int i = 0; i < kStr; ++i) {
+          p.dbg[lane_row * 64 + i] = __uint_as_float(s1[i]);
+          p.dbg[8192 + lane_row * 64 + i] = __uint_as_float(s2[i]);
+        }
+      }
+      // key n visible to query m iff n <= m + off
+      bool need_mask;
+      int lim;  // kDkDv: first visible column (query) index; kDq: last visible column (key) index
+      if constexpr (MODE == kDkDv) {
+        need_mask = p.causal && (r0 + kRes - 1 > x0 + p.causal_off);
+        lim = res_row - p.causal_off - x0;  // column i visible iff i >= lim
+      } else {
+        need_mask = p.causal && (x0 + kStr - 1 > r0 + p.causal_off);
+        lim = res_row + p.causal_off - x0;  // column i visible iff i <= lim
+      }
+      const float* st_l = sStat + (s * 2 + 0) * kStr;
+      const float* st_d = sStat + (s * 2 + 1) * kStr;
+      uint32_t pa[kStr / 2], da[kStr / 2];
+#pragma unroll
+      for (int i = 0; i < kStr; i += 2) {
+        float l0, l1, d0, d1;
+        if constexpr (MODE == kDkDv) {
+          const float2 lv = *reinterpret_cast<const float2*>(st_l + i);
+          const float2 dv = *reinterpret_cast<const float2*>(st_d + i);
+          l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
+        } else {
+          l0 = l1 = my_lse; d0 = d1 = my_delta;
+        }
+        float p0 = fast_exp2(fmaf(__uint_as_float(s1[i]), c, -l0));
+        float p1 = fast_exp2(fmaf(__uint_as_float(s1[i + 1]), c, -l1));
+        if (need_mask) {
+          if constexpr (MODE == kDkDv) {
+            if (i < lim) p0 = 0.f;
+            if (i + 1 < lim) p1 = 0.f;
+          } else {
+            if (i > lim) p0 = 0.f;
+            if (i + 1 > lim) p1 = 0.f;
+          }
+        }
+        const float g0 = p0 * (__uint_as_float(s2[i]) - d0);
+        const float g1 = p1 * (__uint_as_float(s2[i + 1]) - d1);
+        pa[i >> 1] = pack_bf16(p0, p1);
+        da[i >> 1] = pack_bf16(g0, g1);
+      }
+      if constexpr (MODE == kDkDv) tmem_st32(t1, pa);
+      tmem_st32(t2, da);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&a_full[w]);
+    }
+
+    // ---- write-out: accumulators -> scaled fp32 atomics
+    if (n_it > 0) {
+      mbar_wait(acc_full, 0, ctl, 0x700);
+      tc_fence_after_sync();
+      if constexpr (MODE == kDkDv) {
+        const bool ok = res_row < p.Sk;
+        if (w == 0) {
+          float* dst = p.dv_acc + batch * p.dvs[0] + static_cast<int64_t>(res_row) * p.dvs[1] + kv_head * p.dvs[2];
+#pragma unroll
+          for (int cc = 0; cc < 128 / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_addr + C::kAccCol + cc * 32, r);
+            tmem_wait_ld();
+            if (ok) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                atomicAdd(reinterpret_cast<float4*>(dst + cc * 32) + i,
+                          make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                      __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
+            }
+          }
+        } else {
+          float* dst = p.dk_acc + batch * p.dks[0] + static_cast<int64_t>(res_row) * p.dks[1] + kv_head * p.dks[2];
+#pragma unroll
+          for (int cc = 0; cc < DQK / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_addr + C::kAccCol + 128 + cc * 32, r);
+            tmem_wait_ld();
+            if (ok) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                atomicAdd(reinterpret_cast<float4*>(dst + cc * 32) + i,
+                          make_float4(__uint_as_float(r[4 * i]) * p.scale, __uint_as_float(r[4 * i + 1]) * p.scale,
+                                      __uint_as_float(r[4 * i + 2]) * p.scale, __uint_as_float(r[4 * i + 3]) * p.scale));
+            }
+          }
+        }
+      } else {
+        const bool ok = res_row < p.Sq;
+        float* dst = p.dq_acc + batch * p.dqs[0] + static_cast<int64_t>(res_row) * p.dqs[1] + head * p.dqs[2];
+        constexpr int kHalf = DQK / 64;  // 32-column chunks per group
+#pragma unroll
+        for (int cc = w * kHalf; cc < (w + 1) * kHalf; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_addr + C::kAccCol + cc * 32, r);
+          tmem_wait_ld();
+          if (ok) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              atomicAdd(reinterpret_cast<float4*>(dst + cc * 32) + i,
+                        make_float4(__uint_as_float(r[4 * i]) * p.scale, __uint_as_float(r[4 * i + 1]) * p.scale,
+                                    __uint_as_float(r[4 * i + 2]) * p.scale, __uint_as_float(r[4 * i + 3]) * p.scale));
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DQK, int MODE>
+static int launch_bwd(const pith_attn_bwd_args* a, const BwdParams& p, cudaStream_t st) {
+  using C = BwdCfg<DQK, MODE>;
+  CUtensorMap r1, r2, x1, x2;
+  const int qrows = MODE == kDkDv ? kStr : kRes;
+  const int krows = MODE == kDkDv ? kRes : kStr;
+  CUtensorMap tq, tk, tv, tdo;
+  if (int rc = make_tensor_map(&tq, a->q, 2, a->B, a->Sq, a->Hq, a->Dqk, a->q_stride, 64, qrows)) return rc;
+  if (int rc = make_tensor_map(&tdo, a->dout, 2, a->B, a->Sq, a->Hq, a->Dv, a->do_stride, 64, qrows)) return rc;
+  if (int rc = make_tensor_map(&tk, a->k, 2, a->B, a->Sk, a->Hkv, a->Dqk, a->k_stride, 64, krows)) return rc;
+  if (int rc = make_tensor_map(&tv, a->v, 2, a->B, a->Sk, a->Hkv, a->Dv, a->v_stride, 64, krows)) return rc;
+  int tiles;
+  if (MODE == kDkDv) {
+    r1 = tk; r2 = tv; x1 = tq; x2 = tdo;
+    tiles = (a->Sk + kRes - 1) / kRes;
+  } else {
+    r1 = tq; r2 = tdo; x1 = tk; x2 = tv;
+    tiles = (a->Sq + kRes - 1) / kRes;
+  }
+  auto kern = attn_bwd_kernel<DQK, MODE>;
+  PITH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kAlloc));
+  dim3 grid(tiles, a->Hq, a->B);
+  kern<<<grid, kBwdThreads, C::kAlloc, st>>>(r1, r2, x1, x2, p);
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+static bool f32_rows_ok(const void* base, const int64_t st[3]) {
+  return aligned16(base) && st[0] % 4 == 0 && st[1] % 4 == 0 && st[2] % 4 == 0;
+}
+
+}  // namespace pith
+
+using namespace pith;
+
 extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
-  (void)a; (void)stream;
-  return pith::fail(pith::kErrUnsupported, "pith_attn_bwd is not built yet");
+  PITH_REQUIRE(a != nullptr, "null args");
+  PITH_REQUIRE(a->q && a->k && a->v && a->dout && a->lse && a->delta && a->dq_acc && a->dk_acc && a->dv_acc,
+               "null tensor pointer");
+  PITH_REQUIRE(a->B > 0 && a->Sq > 0 && a->Sk > 0 && a->Hq > 0 && a->Hkv > 0, "bad shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d",
+               a->B, a->Sq, a->Sk, a->Hq, a->Hkv);
+  PITH_REQUIRE(a->Hq % a->Hkv == 0, "Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
+  PITH_REQUIRE(a->Dv == 128 && (a->Dqk == 128 || a->Dqk == 192),
+               "unsupported head dims Dqk=%d Dv=%d (supported: 128/128 and 192/128)", a->Dqk, a->Dv);
+  PITH_REQUIRE(a->softmax_scale > 0.f, "softmax_scale must be positive");
+  PITH_REQUIRE(a->Hq <= 65535 && a->B <= 65535, "Hq and B must fit a grid dimension");
+  PITH_REQUIRE(f32_rows_ok(a->dq_acc, a->dq_stride) && f32_rows_ok(a->dk_acc, a->dk_stride) &&
+                   f32_rows_ok(a->dv_acc, a->dv_stride),
+               "gradient accumulators must be 16-byte aligned with 16-byte-multiple strides");
+  if (int rc = require_sm100()) return rc;
+  BwdParams p;
+  p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk_acc = a->dk_acc; p.dv_acc = a->dv_acc;
+  p.dbg = a->debug; p.status = a->status;
+  p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
+  p.causal = a->causal ? 1 : 0; p.causal_off = a->causal_offset;
+  p.scale = a->softmax_scale; p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+  for (int i = 0; i < 3; ++i) { p.dqs[i] = a->dq_stride[i]; p.dks[i] = a->dk_stride[i]; p.dvs[i] = a->dv_stride[i]; }
+  for (int i = 0; i < 2; ++i) { p.ls[i] = a->lse_stride[i]; p.dls[i] = a->delta_stride[i]; }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->Dqk == 128) {
+    if (int rc = launch_bwd<128, kDkDv>(a, p, st)) return rc;
+    return launch_bwd<128, kDq>(a, p, st);
+  }
+  if (int rc = launch_bwd<192, kDkDv>(a, p, st)) return rc;
+  return launch_bwd<192, kDq>(a, p, st);
 }
