@@ -1,0 +1,376 @@
+#!/usr/bin/env python
+"""Benchmark of the context-parallel attention path: causal forward + backward, TFLOP/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+
+N = 1 runs the Qwen3-30B-A3B attention layer at S = 8192 on one GPU; N > 1 (launched with torchrun, one rank
+per GPU) runs the same layer at global S = 32768 under zigzag context parallelism of degree N. One step is one
+forward + backward of the public ring-attention operator on seeded synthetic bf16 inputs. FLOPs follow the
+reference's convention (benchmarks/operators/mla/test_triton.py:7-14): causal forward = B*H*S^2*(Dqk+Dv),
+backward = 2.5 x forward. Rank 0 prints one JSON line.
+
+``--impl reference`` times the reference's CPU attention arithmetic (the oracle's restatement) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "pith-train_b200"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (S_global at N=1, S_global at N>1, Hq, Hkv, Dqk, Dv, description)
+    "qwen3": (8192, 32768, 32, 4, 128, 128, "Qwen3-30B-A3B attention layer, B=1, Hq=32, Hkv=4, head_dim=128"),
+    "mla": (8192, 32768, 16, 16, 192, 128, "DeepSeek-V2-Lite MLA attention, B=1, 16 heads, q/k dim 192, v dim 128"),
+    "long": (16384, 131072, 32, 4, 128, 128, "Qwen3-30B-A3B attention layer, long context"),
+}
+
+
+def fwd_bwd_flops(S, Hq, Dqk, Dv):
+    return 3.5 * Hq * float(S) * S * (Dqk + Dv)
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return {"bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(S_global, Hq, Hkv, Dqk, Dv, cp, rank, sharding, seed=42):
+    """Seeded N(0,1) bf16 Q, K, V, dO at the global shape, sliced to this rank's shard (pinned host tensors)."""
+    from pithtrain_b200.operators.ring_attention import sharding as sh
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for shape in ((1, S_global, Hq, Dqk), (1, S_global, Hkv, Dqk), (1, S_global, Hkv, Dv), (1, S_global, Hq, Dv)):
+        full = torch.randn(shape, generator=g, dtype=torch.float32).bfloat16()
+        loc = sh.shard_sequence(full, cp, rank, sharding).contiguous() if cp > 1 else full
+        out.append(loc.pin_memory() if torch.cuda.is_available() else loc)
+        del full
+    return out
+
+
+def cpu_attention_sample(S, heads, group, Dqk, Dv, seed=42):
+    """The reference's fp32 attention arithmetic, forward + backward, on `heads` query heads (kv heads = heads/group)
+    of a causal sequence of length S, run by the CPU oracle. Returns (seconds, flops)."""
+    from oracle import attention_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    kvh = max(1, heads // group)
+    q = torch.randn(1, S, heads, Dqk, generator=g)
+    k = torch.randn(1, S, kvh, Dqk, generator=g)
+    v = torch.randn(1, S, kvh, Dv, generator=g)
+    do = torch.randn(1, S, heads, Dv, generator=g)
+    t0 = time.perf_counter()
+    O.full_attention_fwd_bwd(q, k, v, do, Dqk ** -0.5)
+    return time.perf_counter() - t0, fwd_bwd_flops(S, heads, Dqk, Dv)
+
+
+def run_reference(args, rank):
+    """Reference arm: CPU attention (oracle port of the reference's PyTorch math) on the host cores."""
+    if rank != 0:
+        return
+    name = args.workload
+    S1, SN, Hq, Hkv, Dqk, Dv, desc = WORKLOADS[name]
+    S = S1 if args.gpus == 1 else SN
+    group = Hq // Hkv
+    # bounded sample: a shorter sequence of the same layer; attention cost grows with S^2, the rate does not
+    S_s, heads = min(S, 2048), min(Hq, group)
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, fl = cpu_attention_sample(S_s, heads, group, Dqk, Dv)
+        if i >= args.warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    tflops = fl / sec / 1e12
+    sample = f"{heads} query heads ({max(1, heads // group)} kv head) x S={S_s} causal fwd+bwd in fp32 per step"
+    line = {
+        "impl": "reference", "metric": "causal fwd+bwd attention TFLOP/s (whole job)", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{desc}; S={S}; CPU sample: {sample}"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample, "host_cpus": os.cpu_count()},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="qwen3")
+    ap.add_argument("--sharding", choices=["zigzag", "contiguous"], default="zigzag")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="skip the comm/compute overlap measurement (N > 1)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus == 1 or world > 1:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun --nproc-per-node {args.gpus}")
+
+    import torch.distributed as dist
+    from pithtrain_b200 import build, kernels
+    from pithtrain_b200.operators.ring_attention import RingAttentionFunc, RingMLAAttentionFunc, _ring
+
+    build.build_library()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    S1, SN, Hq, Hkv, Dqk, Dv, desc = WORKLOADS[args.workload]
+    S = S1 if world == 1 else SN
+    S_loc = S // world
+    scale = Dqk ** -0.5
+    fn = RingMLAAttentionFunc if Dqk == 192 else RingAttentionFunc
+    global_ranks = list(range(world))
+    hq, hk, hv, hdo = make_inputs(S, Hq, Hkv, Dqk, Dv, world, rank, args.sharding)
+    q, k, v, do = (t.to(dev) for t in (hq, hk, hv, hdo))
+
+    def step(q_, k_, v_, do_):
+        q_.grad = k_.grad = v_.grad = None
+        out = fn.apply(q_, k_, v_, scale, rank, world, global_ranks, args.sharding)
+        out.backward(do_)
+        return out, q_.grad, k_.grad, v_.grad
+
+    for t in (q, k, v):
+        t.requires_grad_()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run, steps):
+        """Device time of `steps` calls of run(), max over ranks, in ms per call."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- resident-input measurement (headline `value`)
+    for _ in range(max(3, args.warmup)):
+        step(q, k, v, do)
+    kernels.check_device_status(dev)
+    launches0 = kernels.launch_count
+    with ClockSampler(local_rank) as clk:
+        ms = timed(lambda: step(q, k, v, do), args.steps)
+    launches = (kernels.launch_count - launches0) // args.steps
+    kernels.check_device_status(dev)
+    flops_total = fwd_bwd_flops(S, Hq, Dqk, Dv)
+    tflops_total = flops_total / (ms * 1e-3) / 1e12
+    pk = peaks()
+
+    # ---- end to end through the public operator with host buffers (H2D of inputs, D2H of results, every step)
+    host_out = [torch.empty_like(t).pin_memory() for t in (hdo, hq, hk, hv)]
+
+    def e2e_step():
+        qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+        for t in (qd, kd, vd):
+            t.requires_grad_()
+        res = step(qd, kd, vd, dod)
+        for h, r in zip(host_out, res):
+            h.copy_(r, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, max(3, args.steps // 2))
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    # ---- dominant kernel, timed alone through the C ABI: backward dK/dV (4 of the 5 backward GEMMs)
+    out_d, lse_d = kernels.attn_fwd(q.detach(), k.detach(), v.detach(), scale, True, 0)
+    delta_d = kernels.bwd_preprocess(out_d, do)
+    dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=dev)
+    dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=dev)
+    dq_acc = torch.zeros(q.shape, dtype=torch.float32, device=dev)
+    qd, kd, vd = q.detach(), k.detach(), v.detach()
+    runs = {
+        "attn_fwd_kernel": (lambda: kernels.attn_fwd(qd, kd, vd, scale, True, 0, out=out_d, lse=lse_d), 1.0),
+        "attn_bwd_kernel<kDkDv>": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, None, dk_acc, dv_acc), 2.0),
+        "attn_bwd_kernel<kDq>": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, dq_acc, None, None), 0.5),
+    }
+    kern = {}
+    fwd_fl_local = float(Hq) * S_loc * S_loc * (Dqk + Dv)  # causal forward FLOPs of the local block
+    for name, (run, mult) in runs.items():
+        for _ in range(3):
+            run()
+        kms = timed(run, 10)
+        kern[name] = {"ms": kms, "tflops": mult * fwd_fl_local / (kms * 1e-3) / 1e12}
+    dom = max(kern, key=lambda n: kern[n]["ms"])
+    roofline = {
+        "bound": "tensor", "kernel": dom, "achieved": kern[dom]["tflops"], "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+        "frac": kern[dom]["tflops"] / pk["bf16_tflops"], "peak_source": pk["source"] + " burst (kernel timed alone)",
+        "traffic": None, "kernels": kern,
+        "note": "algorithmic FLOPs per launch: causal block B*H*S^2*(Dqk+Dv) x {fwd 1, dK/dV 2, dQ 0.5}; "
+                "the dQ launch recomputes S and dP (not counted)",
+    }
+
+    # ---- comm / compute overlap of one ring (N > 1): compute alone, exchanges alone, both
+    overlap = None
+    if world > 1 and not args.no_overlap:
+        class NoComm:
+            def exchange(self, send, recv):
+                return None
+
+            @staticmethod
+            def wait(h):
+                return None
+
+        class NoCompute:
+            def fwd_block(self, *a):
+                pass
+
+            def bwd_block(self, *a):
+                pass
+
+            def delta(self, o, d):
+                return torch.empty((o.shape[0], o.shape[2], o.shape[1]), dtype=torch.float32, device=o.device)
+
+            def cast(self, acc):
+                return torch.empty(acc.shape, dtype=torch.bfloat16, device=acc.device)
+
+        be, nocompute = _ring.CudaBlockBackend(), NoCompute()
+        comm, nocomm = _ring.RingComm(rank, world, global_ranks, dev), NoComm()
+
+        def ring(b, c):
+            o, l = _ring.ring_forward(b, c, qd, kd, vd, scale, rank, world, args.sharding)
+            _ring.ring_backward(b, c, qd, kd, vd, o, l, do, scale, rank, world, args.sharding)
+
+        t_both = timed(lambda: ring(be, comm), 5)
+        t_comp = timed(lambda: ring(be, nocomm), 5)
+        t_comm = timed(lambda: ring(nocompute, comm), 5)
+        overlap = {"ms_both": t_both, "ms_compute_only": t_comp, "ms_comm_only": t_comm,
+                   "hidden_fraction": max(0.0, min(1.0, 1.0 - (t_both - t_comp) / t_comm)) if t_comm > 0 else None}
+
+    # ---- CPU baseline (rank 0, N = 1): the oracle on the host cores, bounded sample
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        group = Hq // Hkv
+        heads, S_s = min(Hq, group), 2048
+        cpu_attention_sample(512, heads, group, Dqk, Dv)
+        reps, t_acc, fl = 0, 0.0, 0.0
+        while t_acc < 10.0 and reps < 50:
+            dt, f1 = cpu_attention_sample(S_s, heads, group, Dqk, Dv)
+            t_acc += dt; fl += f1; reps += 1
+        cpu = {"value": fl / t_acc / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+               "host_cpus": os.cpu_count(),
+               "sample": f"{reps} x ({heads} query heads / 1 kv head, S={S_s}) causal fwd+bwd in fp32 with the oracle"}
+
+    if rank == 0:
+        line = {
+            "metric": "causal fwd+bwd attention TFLOP/s (whole job)", "value": tflops_total, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {
+                "workload": f"{desc}; global S={S}, causal; " + (
+                    f"zigzag context parallel CP={world} ({S_loc} tokens per GPU)" if world > 1 and args.sharding == "zigzag"
+                    else f"{args.sharding} CP={world}" if world > 1 else "single GPU (CP=1)"),
+                "sharding": args.sharding if world > 1 else "none",
+                "l2": "inputs + gradients per step exceed the 126 MB L2 (no flush needed)",
+                "flops_convention": "fwd B*H*S^2*(Dqk+Dv), bwd 2.5x fwd",
+            },
+            "tflops_per_gpu": tflops_total / world,
+            "frac_of_measured_bf16_peak": tflops_total / world / pk["bf16_tflops"],
+            "frac_of_nominal_2250": tflops_total / world / 2250.0,
+            "peak_source": pk["source"],
+            "tokens_per_s": S / (ms * 1e-3),
+            "e2e": {"value": flops_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "clocks": clk.summary(),
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+        }
+        if overlap is not None:
+            line["overlap"] = overlap
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -98,8 +98,8 @@ typedef struct pith_attn_bwd_args {
   const void* dout;   /* [B][Sq][Hq][Dv] bf16 */
   const float* lse;   /* [B][Hq][Sq] fp32, log2 domain, of the COMPLETE softmax row */
   const float* delta; /* [B][Hq][Sq] fp32 */
-  float* dq_acc;      /* [B][Sq][Hq][Dqk] fp32, accumulated into (+=) */
-  float* dk_acc;      /* [B][Sk][Hkv][Dqk] fp32, accumulated into (+=) */
+  float* dq_acc;      /* [B][Sq][Hq][Dqk] fp32, accumulated into (+=); NULL = skip dQ */
+  float* dk_acc;      /* [B][Sk][Hkv][Dqk] fp32, accumulated into (+=); NULL (with dv_acc) = skip dK/dV */
   float* dv_acc;      /* [B][Sk][Hkv][Dv] fp32, accumulated into (+=) */
   uint32_t* status;
   float* debug;

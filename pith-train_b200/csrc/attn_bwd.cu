@@ -438,8 +438,11 @@ using namespace pith;
 
 extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   PITH_REQUIRE(a != nullptr, "null args");
-  PITH_REQUIRE(a->q && a->k && a->v && a->dout && a->lse && a->delta && a->dq_acc && a->dk_acc && a->dv_acc,
-               "null tensor pointer");
+  PITH_REQUIRE(a->q && a->k && a->v && a->dout && a->lse && a->delta, "null tensor pointer");
+  const bool want_dq = a->dq_acc != nullptr;
+  const bool want_dkv = a->dk_acc != nullptr;
+  PITH_REQUIRE((a->dk_acc == nullptr) == (a->dv_acc == nullptr), "dk_acc and dv_acc must be given together");
+  PITH_REQUIRE(want_dq || want_dkv, "no gradient accumulator given");
   PITH_REQUIRE(a->B > 0 && a->Sq > 0 && a->Sk > 0 && a->Hq > 0 && a->Hkv > 0, "bad shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d",
                a->B, a->Sq, a->Sk, a->Hq, a->Hkv);
   PITH_REQUIRE(a->Hq % a->Hkv == 0, "Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
@@ -447,8 +450,8 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
                "unsupported head dims Dqk=%d Dv=%d (supported: 128/128 and 192/128)", a->Dqk, a->Dv);
   PITH_REQUIRE(a->softmax_scale > 0.f, "softmax_scale must be positive");
   PITH_REQUIRE(a->Hq <= 65535 && a->B <= 65535, "Hq and B must fit a grid dimension");
-  PITH_REQUIRE(f32_rows_ok(a->dq_acc, a->dq_stride) && f32_rows_ok(a->dk_acc, a->dk_stride) &&
-                   f32_rows_ok(a->dv_acc, a->dv_stride),
+  PITH_REQUIRE((!want_dq || f32_rows_ok(a->dq_acc, a->dq_stride)) &&
+                   (!want_dkv || (f32_rows_ok(a->dk_acc, a->dk_stride) && f32_rows_ok(a->dv_acc, a->dv_stride))),
                "gradient accumulators must be 16-byte aligned with 16-byte-multiple strides");
   if (int rc = require_sm100()) return rc;
   BwdParams p;
@@ -461,9 +464,15 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   for (int i = 0; i < 2; ++i) { p.ls[i] = a->lse_stride[i]; p.dls[i] = a->delta_stride[i]; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->Dqk == 128) {
-    if (int rc = launch_bwd<128, kDkDv>(a, p, st)) return rc;
-    return launch_bwd<128, kDq>(a, p, st);
+    if (want_dkv)
+      if (int rc = launch_bwd<128, kDkDv>(a, p, st)) return rc;
+    if (want_dq)
+      if (int rc = launch_bwd<128, kDq>(a, p, st)) return rc;
+    return kOk;
   }
-  if (int rc = launch_bwd<192, kDkDv>(a, p, st)) return rc;
-  return launch_bwd<192, kDq>(a, p, st);
+  if (want_dkv)
+    if (int rc = launch_bwd<192, kDkDv>(a, p, st)) return rc;
+  if (want_dq)
+    if (int rc = launch_bwd<192, kDq>(a, p, st)) return rc;
+  return kOk;
 }

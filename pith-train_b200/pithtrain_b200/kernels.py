@@ -14,6 +14,9 @@ from ._lib import I64x2, I64x3
 
 _status_words: dict[int, torch.Tensor] = {}
 
+# Kernels of libpith_b200.so enqueued by this process so far (benchmarks report the per-step count).
+launch_count = 0
+
 
 def status_word(device: torch.device) -> torch.Tensor:
     """Per-device uint32 the kernels write to when a bounded wait gives up (0 = healthy)."""
@@ -34,6 +37,11 @@ def check_device_status(device=None) -> None:
         w.zero_()
         text = _lib.load().pith_status_string(val).decode()
         raise RuntimeError(f"pith_b200 kernel reported: {text}")
+
+
+def _count(n: int) -> None:
+    global launch_count
+    launch_count += n
 
 
 def _stream(t: torch.Tensor) -> int:
@@ -92,6 +100,7 @@ def attn_fwd(q, k, v, softmax_scale: float, causal: bool, causal_offset: int = 0
         a.prev_o_stride = _bshd(prev_o, "prev_o")
         a.prev_lse_stride = _bhs(prev_lse, "prev_lse")
     _lib.check(_lib.load().pith_attn_fwd(ctypes.byref(a), _stream(q)), "pith_attn_fwd")
+    _count(1)
     return out, lse
 
 
@@ -106,6 +115,7 @@ def bwd_preprocess(o, dout, delta=None):
     a.B, a.S, a.H, a.Dv = B, S, H, Dv
     a.o_stride, a.do_stride, a.delta_stride = _bshd(o, "o"), _bshd(dout, "dout"), _bhs(delta, "delta")
     _lib.check(_lib.load().pith_attn_bwd_preprocess(ctypes.byref(a), _stream(o)), "pith_attn_bwd_preprocess")
+    _count(1 if o.numel() else 0)
     return delta
 
 
@@ -116,21 +126,27 @@ def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool,
     B, Sq, Hq, Dqk = q.shape
     _, Sk, Hkv, Dv = v.shape
     for t, n in ((dq_acc, "dq_acc"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
-        if t.dtype != torch.float32:
+        if t is not None and t.dtype != torch.float32:
             raise TypeError(f"{n} must be float32")
     a = _lib.AttnBwdArgs()
     a.q, a.k, a.v, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
     a.lse, a.delta = lse_log2.data_ptr(), delta.data_ptr()
-    a.dq_acc, a.dk_acc, a.dv_acc = dq_acc.data_ptr(), dk_acc.data_ptr(), dv_acc.data_ptr()
+    a.dq_acc = dq_acc.data_ptr() if dq_acc is not None else None
+    a.dk_acc = dk_acc.data_ptr() if dk_acc is not None else None
+    a.dv_acc = dv_acc.data_ptr() if dv_acc is not None else None
     a.status = status_word(q.device).data_ptr()
     a.debug = debug.data_ptr() if debug is not None else None
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
     a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), 0
     a.softmax_scale = float(softmax_scale)
     a.q_stride, a.k_stride, a.v_stride, a.do_stride = _bshd(q, "q"), _bshd(k, "k"), _bshd(v, "v"), _bshd(dout, "dout")
-    a.dq_stride, a.dk_stride, a.dv_stride = _bshd(dq_acc, "dq_acc"), _bshd(dk_acc, "dk_acc"), _bshd(dv_acc, "dv_acc")
+    if dq_acc is not None:
+        a.dq_stride = _bshd(dq_acc, "dq_acc")
+    if dk_acc is not None:
+        a.dk_stride, a.dv_stride = _bshd(dk_acc, "dk_acc"), _bshd(dv_acc, "dv_acc")
     a.lse_stride, a.delta_stride = _bhs(lse_log2, "lse"), _bhs(delta, "delta")
     _lib.check(_lib.load().pith_attn_bwd(ctypes.byref(a), _stream(q)), "pith_attn_bwd")
+    _count((dq_acc is not None) + (dk_acc is not None))
 
 
 def cast_to_bf16(acc, out=None, scale: float = 1.0):
@@ -142,6 +158,7 @@ def cast_to_bf16(acc, out=None, scale: float = 1.0):
     _lib.check(_lib.load().pith_cast_f32_to_bf16(acc.data_ptr(), out.data_ptr(), B, S, H, D, _bshd(acc, "acc"),
                                                  _bshd(out, "out"), float(scale), _stream(acc)),
                "pith_cast_f32_to_bf16")
+    _count(1 if acc.numel() else 0)
     return out
 
 
@@ -163,4 +180,5 @@ def combine(out1, lse1, out2, lse2, natural: bool):
     a.out1_stride, a.out2_stride = _bshd(out1, "out1"), _bshd(out2, "out2")
     a.lse1_stride, a.lse2_stride = _bhs(lse1, "lse1"), _bhs(lse2, "lse2")
     _lib.check(_lib.load().pith_combine(ctypes.byref(a), _stream(out1)), "pith_combine")
+    _count(1 if out1.numel() else 0)
     return out, lse

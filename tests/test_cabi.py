@@ -1,0 +1,84 @@
+"""The C-ABI library: builds, loads on a machine without a GPU, exports what the header declares, and rejects
+bad arguments on the host with a message (no kernel is launched here)."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "pith_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pith_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_all_exported(built_library):
+    from pithtrain_b200 import _lib
+    lib = ctypes.CDLL(str(built_library))
+    names = declared_symbols()
+    assert "pith_attn_fwd" in names and "pith_attn_bwd" in names and "pith_combine" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/pith_b200.h but not exported"
+        assert n in _lib.EXPORTS, f"{n} has no ctypes signature in pithtrain_b200._lib"
+    assert sorted(_lib.EXPORTS) == names
+
+
+def test_abi_version_and_status_strings(built_library):
+    from pithtrain_b200 import _lib
+    lib = _lib.load()
+    assert lib.pith_abi_version() == 1
+    assert lib.pith_status_string(0) == b"ok"
+    assert b"timed out" in lib.pith_status_string((1 << 24) | 0x700)
+
+
+def test_struct_sizes_match_the_header(built_library):
+    """ctypes mirrors of the argument structs must have the C layout (checked against a compiled sizeof)."""
+    import subprocess, tempfile, textwrap
+    from pithtrain_b200 import _lib
+    src = textwrap.dedent("""
+        #include <stdio.h>
+        #include "pith_b200.h"
+        int main(void) {
+          printf("%zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
+                 sizeof(pith_attn_bwd_args), sizeof(pith_combine_args));
+          return 0;
+        }""")
+    with tempfile.TemporaryDirectory() as d:
+        (Path(d) / "s.c").write_text(src)
+        subprocess.run(["gcc", "-I", str(ROOT / "include"), str(Path(d) / "s.c"), "-o", str(Path(d) / "s")], check=True)
+        sizes = [int(x) for x in subprocess.run([str(Path(d) / "s")], capture_output=True, text=True, check=True).stdout.split()]
+    assert sizes == [ctypes.sizeof(_lib.AttnFwdArgs), ctypes.sizeof(_lib.BwdPreprocessArgs),
+                     ctypes.sizeof(_lib.AttnBwdArgs), ctypes.sizeof(_lib.CombineArgs)]
+
+
+def test_host_side_rejections(built_library):
+    from pithtrain_b200 import _lib
+    lib = _lib.load()
+    assert lib.pith_attn_fwd(None, None) < 0
+    assert b"null args" in lib.pith_last_error()
+    a = _lib.AttnFwdArgs()
+    assert lib.pith_attn_fwd(ctypes.byref(a), None) < 0
+    assert b"null tensor pointer" in lib.pith_last_error()
+    a.q = a.k = a.v = a.o = a.lse = 0x1000
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = 1, 128, 128, 6, 4, 128, 128
+    a.softmax_scale = 0.1
+    assert lib.pith_attn_fwd(ctypes.byref(a), None) < 0
+    assert b"not a multiple" in lib.pith_last_error()
+    a.Hq, a.Dqk = 8, 96
+    assert lib.pith_attn_fwd(ctypes.byref(a), None) < 0
+    assert b"unsupported head dims" in lib.pith_last_error()
+    c = _lib.CombineArgs()
+    c.out1 = c.out2 = c.lse1 = c.lse2 = c.out = c.lse = 0x1000
+    c.B, c.S, c.H, c.D = 1, 4, 2, 12
+    assert lib.pith_combine(ctypes.byref(c), None) < 0
+    assert b"bad shape" in lib.pith_last_error()
+    b = _lib.AttnBwdArgs()
+    b.q = b.k = b.v = b.dout = b.lse = b.delta = 0x1000
+    assert lib.pith_attn_bwd(ctypes.byref(b), None) < 0
+    assert b"no gradient accumulator" in lib.pith_last_error()
+    with pytest.raises(_lib.PithLibraryError):
+        _lib.check(-1, "demo")

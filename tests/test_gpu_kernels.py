@@ -1,0 +1,305 @@
+"""Parity of the sm_100a kernels, called through the C ABI, against the CPU oracle and the golden vectors.
+
+Tolerances are the path's bars: bf16 tensors max-abs <= 2e-2 and mean-abs <= 2e-3, LSE within 1e-3 (fp32)."""
+
+import math
+
+import pytest
+import torch
+
+from helpers import (GOLDEN, assert_bf16_close, assert_lse_close, load_golden_attention)
+from oracle import attention_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K(cuda_device):
+    from pithtrain_b200 import kernels
+    yield kernels
+    kernels.check_device_status(cuda_device)
+
+
+def _rand(shape, dev, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(shape, generator=g).bfloat16().to(dev)
+
+
+def _inputs(B, Sq, Sk, Hq, Hkv, Dqk, dev, seed=42):
+    return (_rand((B, Sq, Hq, Dqk), dev, seed), _rand((B, Sk, Hkv, Dqk), dev, seed + 1),
+            _rand((B, Sk, Hkv, 128), dev, seed + 2), _rand((B, Sq, Hq, 128), dev, seed + 3))
+
+
+FWD_CASES = [
+    # B, Sq, Sk, Hq, Hkv, Dqk, causal, offset
+    (1, 128, 128, 1, 1, 128, False, 0),
+    (1, 256, 256, 2, 1, 128, True, 0),
+    (1, 1024, 1024, 8, 2, 128, True, 0),       # GQA 4:1
+    (2, 1000, 1000, 4, 4, 128, True, 0),       # ragged tail, batch 2
+    (1, 512, 1024, 8, 1, 128, False, 0),       # GQA 8:1, Sq != Sk
+    (1, 512, 1024, 4, 1, 128, True, 512),      # causal, bottom-right aligned
+    (1, 384, 200, 4, 2, 128, False, 0),        # key tail inside one block
+    (1, 64, 72, 2, 2, 128, True, 8),           # smaller than one tile
+    (1, 768, 256, 2, 1, 128, True, -512),      # early queries see nothing: O = 0, LSE = -inf
+    (1, 2048, 2048, 4, 4, 192, True, 0),       # MLA head dims
+    (1, 512, 520, 16, 16, 192, False, 0),
+    (1, 1, 1, 1, 1, 128, True, 0),             # single token
+]
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,Dqk,causal,off", FWD_CASES)
+def test_forward_matches_oracle(K, cuda_device, B, Sq, Sk, Hq, Hkv, Dqk, causal, off):
+    q, k, v, _ = _inputs(B, Sq, Sk, Hq, Hkv, Dqk, cuda_device)
+    scale = Dqk ** -0.5
+    out, lse = K.attn_fwd(q, k, v, scale, causal, off)
+    ro, rl = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, causal, off)
+    assert out.dtype == torch.bfloat16 and lse.dtype == torch.float32
+    assert_bf16_close(out, ro, "O")
+    assert_lse_close(lse, rl)
+    K.check_device_status(cuda_device)
+
+
+BWD_CASES = [
+    (1, 128, 128, 1, 1, 128, False, 0),
+    (1, 256, 256, 2, 1, 128, True, 0),
+    (1, 1024, 1024, 8, 2, 128, True, 0),
+    (2, 1000, 1000, 4, 4, 128, True, 0),
+    (1, 512, 1024, 8, 1, 128, False, 0),
+    (1, 512, 1024, 4, 1, 128, True, 512),
+    (1, 384, 200, 4, 2, 128, False, 0),
+    (1, 768, 256, 2, 1, 128, True, -512),
+    (1, 2048, 2048, 4, 4, 192, True, 0),
+    (1, 1000, 520, 2, 2, 192, False, 0),
+    (1, 1, 1, 1, 1, 128, True, 0),
+]
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,Dqk,causal,off", BWD_CASES)
+def test_backward_matches_oracle(K, cuda_device, B, Sq, Sk, Hq, Hkv, Dqk, causal, off):
+    q, k, v, do = _inputs(B, Sq, Sk, Hq, Hkv, Dqk, cuda_device)
+    scale = Dqk ** -0.5
+    out, lse = K.attn_fwd(q, k, v, scale, causal, off)
+    delta = K.bwd_preprocess(out, do)
+    dq = torch.zeros(q.shape, device=cuda_device)
+    dk = torch.zeros(k.shape, device=cuda_device)
+    dv = torch.zeros(v.shape, device=cuda_device)
+    K.attn_bwd(q, k, v, do, lse, delta, scale, causal, off, dq, dk, dv)
+    ro, rl = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, causal, off)
+    rd = O.delta(ro, do.cpu())
+    assert torch.allclose(delta.cpu(), O.delta(out.cpu(), do.cpu()), atol=1e-4, rtol=1e-5)
+    rdq, rdk, rdv = O.attention_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), rl, rd, scale, causal, off)
+    for acc, ref, name in ((dq, rdq, "dQ"), (dk, rdk, "dK"), (dv, rdv, "dV")):
+        assert_bf16_close(acc, ref, name + " (fp32 accumulator)")
+        assert_bf16_close(K.cast_to_bf16(acc), ref, name)
+    K.check_device_status(cuda_device)
+
+
+def test_backward_accumulates_and_can_skip_halves(K, cuda_device):
+    q, k, v, do = _inputs(1, 256, 256, 4, 2, 128, cuda_device)
+    scale = 128 ** -0.5
+    out, lse = K.attn_fwd(q, k, v, scale, True, 0)
+    delta = K.bwd_preprocess(out, do)
+    z = lambda t: torch.zeros(t.shape, device=cuda_device)  # noqa: E731
+    dq, dk, dv = z(q), z(k), z(v)
+    K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, dq, dk, dv)
+    dq2, dk2, dv2 = dq.clone(), dk.clone(), dv.clone()
+    K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, dq2, None, None)     # dQ only, accumulating
+    K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, None, dk2, dv2)      # dK/dV only
+    for a, b in ((dq2, dq), (dk2, dk), (dv2, dv)):
+        assert torch.allclose(a, 2 * b, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["mla_causal", "mla_full", "d128_causal"])
+def test_golden_vectors(K, cuda_device, name):
+    g = load_golden_attention(name)
+    q, k, v, do = (g[x].to(cuda_device) for x in ("q", "k", "v", "do"))
+    out, lse = K.attn_fwd(q, k, v, g["scale"], g["causal"], 0)
+    assert_bf16_close(out, g["o"], "O")
+    delta = K.bwd_preprocess(out, do)
+    dq, dk, dv = (torch.zeros(t.shape, device=cuda_device) for t in (q, k, v))
+    K.attn_bwd(q, k, v, do, lse, delta, g["scale"], g["causal"], 0, dq, dk, dv)
+    assert_bf16_close(dq, g["dq"], "dQ")
+    assert_bf16_close(dk, g["dk"], "dK")
+    assert_bf16_close(dv, g["dv"], "dV")
+
+
+def test_fused_merge_equals_separate_combine(K, cuda_device):
+    """Attention over two KV halves: the second call merges into the first in its epilogue."""
+    q, k, v, _ = _inputs(1, 512, 1024, 8, 2, 128, cuda_device)
+    scale = 128 ** -0.5
+    acc, lse = K.attn_fwd(q, k[:, :512], v[:, :512], scale, False, 0, out_fp32=True)
+    o2, l2 = K.attn_fwd(q, k[:, 512:], v[:, 512:], scale, False, 0, out_fp32=True)
+    ref_o, ref_l = K.combine(acc, lse, o2, l2, natural=False)
+    K.attn_fwd(q, k[:, 512:], v[:, 512:], scale, False, 0, out=acc, lse=lse, prev_o=acc, prev_lse=lse)
+    assert torch.allclose(acc, ref_o, atol=2e-6, rtol=1e-5)
+    assert torch.allclose(lse, ref_l, atol=1e-5)
+    full_o, full_l = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, False, 0)
+    assert_bf16_close(acc, full_o, "merged O")
+    assert_lse_close(lse, full_l)
+
+
+def test_natural_log_lse_flag(K, cuda_device):
+    q, k, v, _ = _inputs(1, 256, 256, 2, 2, 128, cuda_device)
+    _, l2 = K.attn_fwd(q, k, v, 0.1, True, 0)
+    _, ln = K.attn_fwd(q, k, v, 0.1, True, 0, lse_natural=True)
+    assert torch.allclose(ln, l2 * math.log(2.0), atol=1e-5)
+
+
+# ------------------------------------------------------------------ combine (tests/test_online_softmax_combine_log2.py)
+def test_combine_golden(K, cuda_device):
+    import numpy as np
+    z = np.load(GOLDEN / "golden_combine.npz")
+    t = {k: torch.from_numpy(z[k]).to(cuda_device) for k in z.files}
+    for natural, suffix in ((True, "nat"), (False, "log2")):
+        for out2 in (t["out2"], t["out2"].bfloat16()):
+            out, lse = K.combine(t["out1"], t["lse1"], out2, t["lse2"], natural=natural)
+            assert torch.allclose(out, t[f"out_{suffix}"], atol=1e-5, equal_nan=True)
+            assert torch.allclose(lse, t[f"lse_{suffix}"], atol=1e-5, equal_nan=True)
+
+
+def test_combine_two_halves_identity_commutativity(cuda_device):
+    from pithtrain_b200.operators.mla import _mla_fwd
+    from pithtrain_b200.operators.ring_attention import _online_softmax_combine, _online_softmax_combine_log2
+    B, S, H = 1, 256, 16
+    q, k, v, _ = _inputs(B, S // 2, S, H, H, 192, cuda_device, seed=123)
+    scale = 192 ** -0.5
+    o1, l1 = _mla_fwd(q, k[:, :128], v[:, :128], scale, causal=False)
+    o2, l2 = _mla_fwd(q, k[:, 128:], v[:, 128:], scale, causal=False)
+    co, cl = _online_softmax_combine_log2(o1, l1, o2, l2)
+    assert co.dtype == torch.float32 and co.is_contiguous()
+    ro, rl = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, False)
+    assert_bf16_close(co, ro, "two halves")
+    assert_lse_close(cl, rl)
+    # identity: merging with an empty partial (LSE = -inf) changes nothing
+    io, il = _online_softmax_combine_log2(o1, l1, torch.zeros_like(o1), torch.full_like(l1, float("-inf")))
+    assert torch.allclose(io, o1.float(), atol=1e-5) and torch.allclose(il, l1, atol=1e-5)
+    # commutativity
+    ab = _online_softmax_combine_log2(o1, l1, o2, l2)
+    ba = _online_softmax_combine_log2(o2, l2, o1, l1)
+    assert torch.allclose(ab[0], ba[0], atol=1e-5) and torch.allclose(ab[1], ba[1], atol=1e-5)
+    # natural-log variant agrees after converting the LSEs
+    no, nl = _online_softmax_combine(o1, l1 * math.log(2.0), o2, l2 * math.log(2.0))
+    assert torch.allclose(no, co, atol=1e-5) and torch.allclose(nl, cl * math.log(2.0), atol=1e-4)
+    # empty input
+    e = torch.empty(1, 0, 2, 128, device=cuda_device)
+    eo, el = _online_softmax_combine_log2(e, torch.empty(1, 2, 0, device=cuda_device), e, torch.empty(1, 2, 0, device=cuda_device))
+    assert eo.shape == (1, 0, 2, 128) and el.shape == (1, 2, 0)
+
+
+# ------------------------------------------------------------------ operator layer (CP = 1)
+def test_custom_op_autograd_and_mla_module(cuda_device):
+    from pithtrain_b200.operators.attention import flash_attn_func
+    from pithtrain_b200.operators.mla import MLA
+    q, k, v, do = _inputs(1, 512, 512, 8, 2, 128, cuda_device)
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    out = flash_attn_func(q, k, v, softmax_scale=128 ** -0.5, causal=True)
+    out.backward(do)
+    ref = O.full_attention_fwd_bwd(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(), 128 ** -0.5)
+    assert_bf16_close(out, ref["o"], "O")
+    assert_bf16_close(q.grad, ref["dq"], "dQ")
+    assert_bf16_close(k.grad, ref["dk"], "dK")
+    assert_bf16_close(v.grad, ref["dv"], "dV")
+    q, k, v, do = _inputs(1, 256, 256, 16, 16, 192, cuda_device)
+    q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
+    MLA.autotune(1, 256, 16, 192, 128, 192 ** -0.5)
+    out = MLA(16, 192, 128)(q, k, v)
+    out.backward(do)
+    ref = O.full_attention_fwd_bwd(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), do.cpu(), 192 ** -0.5)
+    assert_bf16_close(out, ref["o"], "MLA O")
+    assert_bf16_close(q.grad, ref["dq"], "MLA dQ")
+    assert_bf16_close(k.grad, ref["dk"], "MLA dK")
+    assert_bf16_close(v.grad, ref["dv"], "MLA dV")
+
+
+def test_mla_helpers_match_reference_decomposition(cuda_device):
+    from pithtrain_b200.operators.mla import _mla_bwd_dk_dv, _mla_bwd_dq, _mla_bwd_preprocess, _mla_fwd
+    q, k, v, do = _inputs(2, 512, 512, 16, 16, 192, cuda_device)
+    scale = 192 ** -0.5
+    for causal in (True, False):
+        out, lse = _mla_fwd(q, k, v, scale, causal=causal)
+        delta = _mla_bwd_preprocess(out, do)
+        dk, dv = _mla_bwd_dk_dv(q, k, v, do, lse, delta, scale, causal=causal)
+        dq = _mla_bwd_dq(q, k, v, do, lse, delta, scale, causal=causal)
+        ro, rl = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, causal)
+        rdq, rdk, rdv = O.attention_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), rl, O.delta(ro, do.cpu()), scale, causal)
+        assert_bf16_close(out, ro, "O"); assert_lse_close(lse, rl)
+        assert_bf16_close(dq, rdq, "dQ"); assert_bf16_close(dk, rdk, "dK"); assert_bf16_close(dv, rdv, "dV")
+
+
+# ------------------------------------------------------------------ full size (Qwen3-30B-A3B layer, S = 8192)
+@pytest.fixture(scope="module")
+def qwen3_full(K, cuda_device):
+    q, k, v, do = _inputs(1, 8192, 8192, 32, 4, 128, cuda_device, seed=42)
+    scale = 128 ** -0.5
+    out, lse = K.attn_fwd(q, k, v, scale, True, 0)
+    delta = K.bwd_preprocess(out, do)
+    dq, dk, dv = (torch.zeros(t.shape, device=cuda_device) for t in (q, k, v))
+    K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, dq, dk, dv)
+    return dict(q=q, k=k, v=v, do=do, scale=scale, out=out, lse=lse, delta=delta, dq=dq, dk=dk, dv=dv)
+
+
+def test_full_size_slices_match_oracle(qwen3_full):
+    """Rows whose dependencies are small enough for the CPU: the first 256 queries (keys 0..255 only) and the last
+    128 queries of two heads against all 8192 keys."""
+    f = qwen3_full
+    q, k, v = f["q"].cpu(), f["k"].cpu(), f["v"].cpu()
+    ro, rl = O.attention_fwd(q[:, :256], k[:, :256], v[:, :256], f["scale"], True, 0)
+    assert_bf16_close(f["out"][:, :256], ro, "O[:256]")
+    assert_lse_close(f["lse"][:, :, :256], rl)
+    heads = [5, 31]
+    kv = [h // 8 for h in heads]
+    ro, rl = O.attention_fwd(q[:, -128:, heads], k[:, :, kv], v[:, :, kv], f["scale"], True, 8192 - 128)
+    assert_bf16_close(f["out"][:, -128:, heads], ro, "O[-128:]")
+    assert_lse_close(f["lse"][:, heads, -128:], rl)
+    # gradients of the last 128 keys depend on the last 128 queries only
+    do = f["do"].cpu()
+    o_full, l_full = f["out"].cpu().float(), f["lse"].cpu()
+    dl = O.delta(o_full[:, -128:], do[:, -128:])
+    _, rdk, rdv = O.attention_bwd(q[:, -128:], k[:, -128:], v[:, -128:], do[:, -128:], l_full[:, :, -128:], dl,
+                                  f["scale"], True, 0)
+    assert_bf16_close(f["dk"][:, -128:], rdk, "dK[-128:]")
+    assert_bf16_close(f["dv"][:, -128:], rdv, "dV[-128:]")
+    # dQ of the first 256 queries depends on the first 256 keys only
+    dl = O.delta(o_full[:, :256], do[:, :256])
+    rdq, _, _ = O.attention_bwd(q[:, :256], k[:, :256], v[:, :256], do[:, :256], l_full[:, :, :256], dl,
+                                f["scale"], True, 0)
+    assert_bf16_close(f["dq"][:, :256], rdq, "dQ[:256]")
+
+
+def test_full_size_properties(K, cuda_device, qwen3_full):
+    f = qwen3_full
+    # softmax rows sum to one: V = 1 gives O = 1 up to bf16 rounding of P
+    ones = torch.ones_like(f["v"])
+    o1, _ = K.attn_fwd(f["q"], f["k"], ones, f["scale"], True, 0)
+    assert (o1.float() - 1).abs().max().item() <= 8e-3
+    # scaling V by 2 scales O by exactly 2 (powers of two are exact in bf16 and fp32)
+    o2, l2 = K.attn_fwd(f["q"], f["k"], f["v"] * 2, f["scale"], True, 0)
+    assert torch.equal(o2, f["out"] * 2) and torch.equal(l2, f["lse"])
+    # the backward is linear in dO
+    do2 = f["do"] * 2
+    delta2 = K.bwd_preprocess(f["out"], do2)
+    assert torch.equal(delta2, f["delta"] * 2)
+    dq, dk, dv = (torch.zeros_like(f[n]) for n in ("dq", "dk", "dv"))
+    K.attn_bwd(f["q"], f["k"], f["v"], do2, f["lse"], delta2, f["scale"], True, 0, dq, dk, dv)
+    for a, n in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        err = (a - 2 * f[n]).abs().max().item()
+        assert err <= 1e-3 * f[n].abs().max().item(), (n, err)   # fp32 atomics: summation order differs per run
+    # sum over queries of dO equals... dV column sums: sum_n dV[n] = sum_m dO[m] per kv-head group (rows of P sum to 1)
+    g = f["do"].float().view(1, 8192, 4, 8, 128).sum(dim=(1, 3))
+    assert torch.allclose(f["dv"].sum(dim=1), g, rtol=2e-2, atol=0.5)
+    K.check_device_status(cuda_device)
+
+
+def test_full_size_against_flash_attn(qwen3_full):
+    """flash-attn is the arithmetic behind the reference's GQA path (ring_attention/standard.py:26,:91,:134)."""
+    fa = pytest.importorskip("flash_attn")
+    f = qwen3_full
+    q, k, v = (f[n].clone().requires_grad_() for n in ("q", "k", "v"))
+    out, lse, _ = fa.flash_attn_func(q, k, v, softmax_scale=f["scale"], causal=True, return_attn_probs=True)
+    out.backward(f["do"])
+    K = __import__("pithtrain_b200.kernels", fromlist=["x"])
+    assert_bf16_close(f["out"], out, "O vs flash-attn")
+    assert_lse_close(f["lse"] * math.log(2.0), lse, "LSE vs flash-attn (natural log)")
+    assert_bf16_close(K.cast_to_bf16(f["dq"]), q.grad, "dQ vs flash-attn")
+    assert_bf16_close(K.cast_to_bf16(f["dk"]), k.grad, "dK vs flash-attn")
+    assert_bf16_close(K.cast_to_bf16(f["dv"]), v.grad, "dV vs flash-attn")

@@ -1,0 +1,104 @@
+"""The CPU oracle against the golden vectors produced by the reference's own code, and against itself."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import GOLDEN, load_golden_attention
+from oracle import attention_oracle as O
+
+
+def test_combine_matches_reference_golden():
+    z = np.load(GOLDEN / "golden_combine.npz")
+    t = {k: torch.from_numpy(z[k]) for k in z.files}
+    for log2, suffix in ((False, "nat"), (True, "log2")):
+        out, lse = O.combine(t["out1"], t["lse1"], t["out2"], t["lse2"], log2=log2)
+        assert torch.allclose(out, t[f"out_{suffix}"], rtol=0, atol=1e-6, equal_nan=True)
+        assert torch.allclose(lse, t[f"lse_{suffix}"], rtol=0, atol=1e-6, equal_nan=True)
+
+
+@pytest.mark.parametrize("name", ["mla_causal", "mla_full", "d128_causal"])
+def test_attention_matches_reference_golden(name):
+    g = load_golden_attention(name)
+    q, k, v, do = (g[x].float() for x in ("q", "k", "v", "do"))
+    o, lse = O.attention_fwd(q, k, v, g["scale"], g["causal"])
+    assert torch.allclose(o, g["o"], rtol=1e-5, atol=2e-6)
+    dl = O.delta(o, do)
+    dq, dk, dv = O.attention_bwd(q, k, v, do, lse, dl, g["scale"], g["causal"])
+    assert torch.allclose(dq, g["dq"], rtol=1e-4, atol=2e-5)
+    assert torch.allclose(dk, g["dk"], rtol=1e-4, atol=2e-5)
+    assert torch.allclose(dv, g["dv"], rtol=1e-4, atol=2e-5)
+
+
+def _config1():
+    """B=1, S=1024, Hq=8, Hkv=2, D=64, N(0,1) from seed 0, scale 1/sqrt(64)."""
+    torch.manual_seed(0)
+    q = torch.randn(1, 1024, 8, 64)
+    k = torch.randn(1, 1024, 2, 64)
+    v = torch.randn(1, 1024, 2, 64)
+    do = torch.randn(1, 1024, 8, 64)
+    return q, k, v, do, 64 ** -0.5
+
+
+def test_config1_split_kv_combine_equals_full_attention():
+    """KV split into two chunks, each attended separately, merged with the log2 combine, equals full attention
+    for O, LSE, dQ, dK and dV."""
+    q, k, v, do, scale = _config1()
+    full = O.full_attention_fwd_bwd(q, k, v, do, scale)
+    # the second chunk is entirely in the future of the first 512 queries: rows with no visible key give LSE=-inf
+    o1, l1 = O.attention_fwd(q, k[:, :512], v[:, :512], scale, True, 0)
+    o2, l2 = O.attention_fwd(q, k[:, 512:], v[:, 512:], scale, True, -512)
+    o, lse = O.combine(o1, l1, o2, l2, log2=True)
+    assert torch.allclose(o, full["o"], atol=2e-6)
+    assert torch.allclose(lse, full["lse_log2"], atol=1e-5)
+    dl = O.delta(o, do)
+    dq1, dk1, dv1 = O.attention_bwd(q, k[:, :512], v[:, :512], do, lse, dl, scale, True, 0)
+    dq2, dk2, dv2 = O.attention_bwd(q, k[:, 512:], v[:, 512:], do, lse, dl, scale, True, -512)
+    assert torch.allclose(dq1 + dq2, full["dq"], atol=2e-5)
+    assert torch.allclose(torch.cat([dk1, dk2], 1), full["dk"], atol=2e-5)
+    assert torch.allclose(torch.cat([dv1, dv2], 1), full["dv"], atol=2e-5)
+
+
+def test_backward_formulas_match_autograd():
+    torch.manual_seed(3)
+    q = torch.randn(2, 64, 4, 32, dtype=torch.float64, requires_grad=True)
+    k = torch.randn(2, 64, 2, 32, dtype=torch.float64, requires_grad=True)
+    v = torch.randn(2, 64, 2, 16, dtype=torch.float64, requires_grad=True)
+    do = torch.randn(2, 64, 4, 16, dtype=torch.float64)
+    o, _ = O.attention_fwd(q, k, v, 0.2, True, 0, torch.float64)
+    o.backward(do)
+    r = O.full_attention_fwd_bwd(q.detach(), k.detach(), v.detach(), do, 0.2, torch.float64)
+    for a, b in ((r["dq"], q.grad), (r["dk"], k.grad), (r["dv"], v.grad)):
+        assert torch.allclose(a, b, atol=1e-10)
+
+
+@pytest.mark.parametrize("cp", [2, 4])
+def test_ring_schedules_equal_full_attention(cp):
+    torch.manual_seed(42)
+    S = 128
+    q = torch.randn(1, S, 4, 32, dtype=torch.float64)
+    k = torch.randn(1, S, 2, 32, dtype=torch.float64)
+    v = torch.randn(1, S, 2, 32, dtype=torch.float64)
+    do = torch.randn(1, S, 4, 32, dtype=torch.float64)
+    full = O.full_attention_fwd_bwd(q, k, v, do, 0.3, torch.float64)
+    idx = [O.contiguous_indices(S, cp, r) for r in range(cp)]
+    outs, _ = O.ring_contiguous_fwd([q[:, i] for i in idx], [k[:, i] for i in idx], [v[:, i] for i in idx], 0.3,
+                                    log2=True, dtype=torch.float64)
+    for r in range(cp):
+        assert torch.allclose(outs[r], full["o"][:, idx[r]], atol=1e-12)
+    idx = [O.zigzag_indices(S, cp, r) for r in range(cp)]
+    sh = lambda t: [t[:, i] for i in idx]  # noqa: E731
+    outs, lses = O.ring_zigzag_fwd(sh(q), sh(k), sh(v), 0.3, torch.float64)
+    dqs, dks, dvs = O.ring_zigzag_bwd(sh(q), sh(k), sh(v), sh(do), outs, lses, 0.3, torch.float64)
+    for r in range(cp):
+        assert torch.allclose(outs[r], full["o"][:, idx[r]], atol=1e-12)
+        assert torch.allclose(lses[r], full["lse_log2"][:, :, idx[r]], atol=1e-12)
+        assert torch.allclose(dqs[r], full["dq"][:, idx[r]], atol=1e-12)
+        assert torch.allclose(dks[r], full["dk"][:, idx[r]], atol=1e-12)
+        assert torch.allclose(dvs[r], full["dv"][:, idx[r]], atol=1e-12)
+
+
+def test_flop_conventions():
+    # Qwen3-30B-A3B attention at S=8192: 5.498e11 forward, x3.5 for forward + backward
+    assert abs(O.fwd_flops(1, 32, 8192, 128, 128) - 5.498e11) / 5.498e11 < 1e-3
+    assert abs(O.fwd_bwd_flops(1, 32, 8192, 128, 128) - 1.924e12) / 1.924e12 < 1e-3

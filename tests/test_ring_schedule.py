@@ -1,0 +1,112 @@
+"""The ring schedule (forward and backward, contiguous and zigzag) with the oracle doing the block arithmetic:
+in-process with simulated ranks, and as real ``torch.distributed`` ranks over gloo on CPU."""
+
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import OracleBlockBackend, ThreadRing
+from oracle import attention_oracle as O
+from pithtrain_b200.operators.ring_attention import _ring
+from pithtrain_b200.operators.ring_attention import sharding as sh
+
+
+def _problem(S, hq=4, hkv=2, dqk=32, dv=16, seed=42, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(1, S, hq, dqk, generator=g, dtype=dtype)
+    k = torch.randn(1, S, hkv, dqk, generator=g, dtype=dtype)
+    v = torch.randn(1, S, hkv, dv, generator=g, dtype=dtype)
+    do = torch.randn(1, S, hq, dv, generator=g, dtype=dtype)
+    return q, k, v, do
+
+
+def _rank_fwd_bwd(rank, cp, comm, layout, q, k, v, do, scale, dtype):
+    be = OracleBlockBackend(dtype)
+    loc = lambda t: sh.shard_sequence(t, cp, rank, layout).contiguous()  # noqa: E731
+    ql, kl, vl, dol = loc(q), loc(k), loc(v), loc(do)
+    out, lse = _ring.ring_forward(be, comm, ql, kl, vl, scale, rank, cp, layout)
+    dq, dk, dv = _ring.ring_backward(be, comm, ql, kl, vl, out, lse, dol, scale, rank, cp, layout)
+    return out, lse, dq, dk, dv
+
+
+def _check_against_full(results, cp, layout, q, k, v, do, scale, atol):
+    full = O.full_attention_fwd_bwd(q, k, v, do, scale, torch.float64)
+    for name, i, dim in (("o", 0, 1), ("lse_log2", 1, 2), ("dq", 2, 1), ("dk", 3, 1), ("dv", 4, 1)):
+        got = sh.unshard_sequence([r[i].double() for r in results], layout, seq_dim=dim)
+        assert torch.allclose(got, full[name], atol=atol), (layout, cp, name, (got - full[name]).abs().max())
+
+
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+@pytest.mark.parametrize("cp", [1, 2, 3, 4, 8])
+def test_schedule_in_process(cp, layout):
+    S = 16 * cp * 2
+    q, k, v, do = _problem(S, dtype=torch.float64)
+    ring = ThreadRing(cp)
+    res = ring.run(lambda r, comm: _rank_fwd_bwd(r, cp, comm, layout, q, k, v, do, 0.25, torch.float64))
+    _check_against_full(res, cp, layout, q, k, v, do, 0.25, 5e-6)
+
+
+def test_schedule_mla_shapes_in_process():
+    """q/k width 192, v width 128, 16 heads without grouping (the DeepSeek-V2-Lite attention layout)."""
+    cp, S = 4, 64
+    q, k, v, do = _problem(S, hq=16, hkv=16, dqk=192, dv=128, dtype=torch.float64)
+    res = ThreadRing(cp).run(lambda r, comm: _rank_fwd_bwd(r, cp, comm, "zigzag", q, k, v, do, 192 ** -0.5, torch.float64))
+    _check_against_full(res, cp, "zigzag", q, k, v, do, 192 ** -0.5, 5e-6)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gloo_worker(rank, world, port, layout, path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    try:
+        torch.set_num_threads(1)
+        q, k, v, do = _problem(32 * world)
+        comm = _ring.RingComm(rank, world, list(range(world)), torch.device("cpu"))
+        res = _rank_fwd_bwd(rank, world, comm, layout, q, k, v, do, 0.25, torch.float32)
+        torch.save([t.clone() for t in res], os.path.join(path, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("layout,world", [("zigzag", 2), ("contiguous", 2), ("zigzag", 4)])
+def test_schedule_over_gloo(tmp_path, layout, world):
+    mp.spawn(_gloo_worker, args=(world, _free_port(), layout, str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    q, k, v, do = _problem(32 * world)
+    _check_against_full(res, world, layout, q, k, v, do, 0.25, 2e-5)
+
+
+def _dying_peer_worker(rank, world, port, path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    if rank == 1:
+        os._exit(0)  # leaves between steps, before posting its send
+    comm = _ring.RingComm(rank, world, list(range(world)), torch.device("cpu"))
+    try:
+        comm.wait(comm.exchange(torch.zeros(4), torch.empty(4)))
+        outcome = "completed"
+    except Exception as e:  # noqa: BLE001
+        outcome = f"raised {type(e).__name__}"
+    with open(os.path.join(path, "outcome.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+def test_lost_peer_surfaces_as_an_exception(tmp_path):
+    """A ring neighbour that exits between steps must turn into a Python exception on the survivor,
+    not a hang (host-side failure; no GPU involved)."""
+    mp.spawn(_dying_peer_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "outcome.txt").read_text().startswith("raised")
