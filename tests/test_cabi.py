@@ -76,6 +76,9 @@ def test_host_side_rejections(built_library):
     c.B, c.S, c.H, c.D = 1, 4, 2, 12
     assert lib.pith_combine(ctypes.byref(c), None) < 0
     assert b"bad shape" in lib.pith_last_error()
+    e = _lib.CombineArgs()
+    e.B, e.S, e.H, e.D = 1, 0, 2, 128
+    assert lib.pith_combine(ctypes.byref(e), None) == 0  # empty input: nothing to do, null pointers accepted
     b = _lib.AttnBwdArgs()
     b.q = b.k = b.v = b.dout = b.lse = b.delta = 0x1000
     assert lib.pith_attn_bwd(ctypes.byref(b), None) < 0

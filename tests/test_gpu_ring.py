@@ -25,7 +25,7 @@ def _problem(S, hq, hkv, dqk, seed=42):
 def _check(results, layout, full):
     from pithtrain_b200.operators.ring_attention import sharding as sh
     for name, i, dim in (("o", 0, 1), ("dq", 2, 1), ("dk", 3, 1), ("dv", 4, 1)):
-        got = sh.unshard_sequence([r[i].float().cpu() for r in results], layout, seq_dim=dim)
+        got = sh.unshard_sequence([r[i].cpu() for r in results], layout, seq_dim=dim)  # bf16 outputs
         assert_bf16_close(got, full[name], f"{layout} {name}")
     lse = sh.unshard_sequence([r[1].cpu() for r in results], layout, seq_dim=2)
     assert_lse_close(lse, full["lse_log2"])
@@ -126,7 +126,7 @@ def test_ring_over_nccl(cuda_device, tmp_path):
         q, k, v, do = _problem(512 * world, hq, hkv, dqk)
         full = O.full_attention_fwd_bwd(q, k, v, do, dqk ** -0.5)
         for i, name in enumerate(("o", "dq", "dk", "dv")):
-            got = sh.unshard_sequence([r[tag][i].float() for r in res], layout, seq_dim=1)
+            got = sh.unshard_sequence([r[tag][i] for r in res], layout, seq_dim=1)  # bf16 outputs
             assert_bf16_close(got, full[name], f"{tag} {name}")
             # the reference's own ring test metric (tests/test_ring_attention.py:91): cosine error < 1e-5
             assert O.cosine_error(got, full[name]) < 1e-5, (tag, name)
