@@ -151,6 +151,44 @@ typedef struct pith_combine_args {
  */
 int pith_combine(const pith_combine_args* args, void* stream);
 
+/* Size of the scratch area built into the library for pith_attn_bwd_noalloc (per GPU, held until exit). */
+#define PITH_NOALLOC_SCRATCH_BYTES (32u << 20)
+
+typedef struct pith_attn_bwd_noalloc_args {
+  const void* q;     /* [B][Sq][Hq][Dqk] bf16 */
+  const void* k;     /* [B][Sk][Hkv][Dqk] bf16 */
+  const void* v;     /* [B][Sk][Hkv][Dv] bf16 */
+  const void* o;     /* [B][Sq][Hq][Dv] bf16, the forward's output */
+  const void* dout;  /* [B][Sq][Hq][Dv] bf16 */
+  const float* lse;  /* [B][Hq][Sq] fp32, log2 domain */
+  void* dq;          /* [B][Sq][Hq][Dqk] bf16, written */
+  void* dk;          /* [B][Sk][Hkv][Dqk] bf16, written */
+  void* dv;          /* [B][Sk][Hkv][Dv] bf16, written */
+  uint32_t* status;
+  int32_t B, Sq, Sk, Hq, Hkv, Dqk, Dv;
+  int32_t causal, causal_offset;
+  float softmax_scale;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+  int64_t lse_stride[2];
+} pith_attn_bwd_noalloc_args;
+
+/*
+ * Complete attention backward (delta, dQ, dK, dV in bf16) that allocates no device memory: delta and the
+ * fp32 accumulators live in a PITH_NOALLOC_SCRATCH_BYTES area that is part of the library image.
+ * No counterpart in the reference, whose backward helpers allocate their outputs and temporaries through
+ * PyTorch. Meant for callers that cannot call cudaMalloc or a framework allocator where the backward runs
+ * (frozen memory pools, plugins inside a runtime that owns device allocation, latency-critical loops).
+ *  - Problems needing more scratch than the area holds (see pith_attn_bwd_noalloc_scratch_bytes) are
+ *    rejected with an error.
+ *  - The first call on each device resolves the area's address; make it before any stream capture begins.
+ *  - All calls on a GPU share the area: calls whose GPU work overlaps race. Use one stream or order them.
+ */
+int pith_attn_bwd_noalloc(const pith_attn_bwd_noalloc_args* args, void* stream);
+/* Scratch bytes pith_attn_bwd_noalloc needs for a problem (compare with PITH_NOALLOC_SCRATCH_BYTES). */
+size_t pith_attn_bwd_noalloc_scratch_bytes(int32_t B, int32_t Sq, int32_t Sk, int32_t Hq, int32_t Hkv, int32_t Dqk,
+                                           int32_t Dv);
+
 /* Text of the last host-side rejection on the calling thread. */
 const char* pith_last_error(void);
 /* Human-readable form of a device status word. Returns a pointer to a thread-local buffer. */

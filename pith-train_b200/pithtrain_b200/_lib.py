@@ -60,6 +60,20 @@ class CombineArgs(Structure):
     ]
 
 
+class AttnBwdNoallocArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("dout", c_void_p), ("lse", c_void_p),
+        ("dq", c_void_p), ("dk", c_void_p), ("dv", c_void_p), ("status", c_void_p),
+        ("B", c_int32), ("Sq", c_int32), ("Sk", c_int32), ("Hq", c_int32), ("Hkv", c_int32),
+        ("Dqk", c_int32), ("Dv", c_int32),
+        ("causal", c_int32), ("causal_offset", c_int32), ("softmax_scale", c_float),
+        ("q_stride", I64x3), ("k_stride", I64x3), ("v_stride", I64x3), ("o_stride", I64x3), ("do_stride", I64x3),
+        ("dq_stride", I64x3), ("dk_stride", I64x3), ("dv_stride", I64x3),
+        ("lse_stride", I64x2),
+    ]
+
+
+NOALLOC_SCRATCH_BYTES = 32 << 20
 FWD_O_FP32 = 1
 FWD_LSE_NATURAL = 2
 COMBINE_NATURAL = 1
@@ -74,6 +88,8 @@ EXPORTS = {
     "pith_cast_f32_to_bf16": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                       POINTER(c_int64), POINTER(c_int64), c_float, c_void_p]),
     "pith_combine": (c_int, [POINTER(CombineArgs), c_void_p]),
+    "pith_attn_bwd_noalloc": (c_int, [POINTER(AttnBwdNoallocArgs), c_void_p]),
+    "pith_attn_bwd_noalloc_scratch_bytes": (ctypes.c_size_t, [c_int32] * 7),
     "pith_last_error": (c_char_p, []),
     "pith_status_string": (c_char_p, [c_uint32]),
     "pith_abi_version": (c_int, []),

@@ -43,8 +43,8 @@ def test_struct_sizes_match_the_header(built_library):
         #include <stdio.h>
         #include "pith_b200.h"
         int main(void) {
-          printf("%zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
-                 sizeof(pith_attn_bwd_args), sizeof(pith_combine_args));
+          printf("%zu %zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
+                 sizeof(pith_attn_bwd_args), sizeof(pith_combine_args), sizeof(pith_attn_bwd_noalloc_args));
           return 0;
         }""")
     with tempfile.TemporaryDirectory() as d:
@@ -52,7 +52,8 @@ def test_struct_sizes_match_the_header(built_library):
         subprocess.run(["gcc", "-I", str(ROOT / "include"), str(Path(d) / "s.c"), "-o", str(Path(d) / "s")], check=True)
         sizes = [int(x) for x in subprocess.run([str(Path(d) / "s")], capture_output=True, text=True, check=True).stdout.split()]
     assert sizes == [ctypes.sizeof(_lib.AttnFwdArgs), ctypes.sizeof(_lib.BwdPreprocessArgs),
-                     ctypes.sizeof(_lib.AttnBwdArgs), ctypes.sizeof(_lib.CombineArgs)]
+                     ctypes.sizeof(_lib.AttnBwdArgs), ctypes.sizeof(_lib.CombineArgs),
+                     ctypes.sizeof(_lib.AttnBwdNoallocArgs)]
 
 
 def test_host_side_rejections(built_library):
