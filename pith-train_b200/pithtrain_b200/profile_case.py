@@ -1,0 +1,61 @@
+"""A fixed, small workload for profilers: one causal forward + backward of each attention kernel.
+
+    python -m pithtrain_b200.profile_case [--shape qwen3|mla] [--seq 8192] [--repeat 2]
+
+Launch order per repeat: attn_fwd_kernel, delta_kernel, attn_bwd_kernel<kDkDv>, attn_bwd_kernel<kDq>,
+3 x cast_kernel, combine_kernel. The working set (a few hundred MB) is larger than the 126 MB L2 and far below the
+sizes at which a multi-pass profiler capture gets slow. Prints the CUDA-event time of each launch.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import kernels as K
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", choices=["qwen3", "mla"], default="qwen3")
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--repeat", type=int, default=2)
+    args = ap.parse_args()
+    hq, hkv, dqk = (32, 4, 128) if args.shape == "qwen3" else (16, 16, 192)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(42)
+    S = args.seq
+    q = torch.randn(1, S, hq, dqk, generator=g).bfloat16().to(dev)
+    k = torch.randn(1, S, hkv, dqk, generator=g).bfloat16().to(dev)
+    v = torch.randn(1, S, hkv, 128, generator=g).bfloat16().to(dev)
+    do = torch.randn(1, S, hq, 128, generator=g).bfloat16().to(dev)
+    scale = dqk ** -0.5
+    out = torch.empty(1, S, hq, 128, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(1, hq, S, dtype=torch.float32, device=dev)
+    delta = torch.empty_like(lse)
+    dq, dk, dv = (torch.zeros(t.shape, dtype=torch.float32, device=dev) for t in (q, k, v))
+    acc = torch.randn(1, S, hq, 128, device=dev)
+
+    def timed(name, fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"{name:28s} {e0.elapsed_time(e1) * 1e3:9.1f} us")
+
+    for rep in range(args.repeat):
+        print(f"-- repeat {rep}")
+        timed("attn_fwd_kernel", lambda: K.attn_fwd(q, k, v, scale, True, 0, out=out, lse=lse))
+        timed("delta_kernel", lambda: K.bwd_preprocess(out, do, delta))
+        timed("attn_bwd_kernel<kDkDv>", lambda: K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, None, dk, dv))
+        timed("attn_bwd_kernel<kDq>", lambda: K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, dq, None, None))
+        timed("cast_kernel x3", lambda: (K.cast_to_bf16(dq), K.cast_to_bf16(dk), K.cast_to_bf16(dv)))
+        timed("combine_kernel", lambda: K.combine(acc, lse, out, lse, natural=False))
+    K.check_device_status(dev)
+
+
+if __name__ == "__main__":
+    main()
