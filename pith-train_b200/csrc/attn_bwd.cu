@@ -47,6 +47,8 @@ struct BwdParams {
 };
 
 constexpr int kBwdThreads = 384;
+constexpr int kBwdRegsLo = 72;   // producer / MMA-issuer warpgroup
+constexpr int kBwdRegsHi = 208;  // compute warpgroups (128 * 72 + 256 * 208 <= 65536)
 constexpr int kRes = 128;  // rows of the resident tile (= TMEM lanes)
 constexpr int kStr = 64;   // rows of a streamed tile (= columns of T1 / T2)
 
@@ -146,6 +148,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
+    setmaxnreg_dec<kBwdRegsLo>();
     if (n_it > 0) {
       if (lane == 0) {
         tma_prefetch_desc(&tm_r1);
@@ -175,7 +178,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             tma_load_4d(sX2 + s * C::kX2 + sub * (kStr * 128), &tm_x2, &x_full[s], sub * 64, x_head, x0, batch);
         }
         if constexpr (MODE == kDkDv) {
-          // statistics of the 64 streamed queries: lse (+inf where the row does not exist or saw no key), delta
+          // statistics of the 64 streamed queries: -lse (-inf where the row does not exist or saw no key), -delta
 #pragma unroll
           for (int r = lane; r < kStr; r += 32) {
             const int m = x0 + r;
@@ -185,8 +188,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
               d = p.delta[batch * p.dls[0] + head * p.dls[1] + m];
               if (l == -INFINITY) l = INFINITY;
             }
-            sStat[(s * 2 + 0) * kStr + r] = l;
-            sStat[(s * 2 + 1) * kStr + r] = d;
+            sStat[(s * 2 + 0) * kStr + r] = -l;  // stored negated: the consumers only ever add them
+            sStat[(s * 2 + 1) * kStr + r] = -d;
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&x_full[s]);
@@ -195,28 +198,35 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    setmaxnreg_dec<kBwdRegsLo>();
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(kRes, kStr, false, false);
       constexpr uint32_t idesc_dv = make_idesc_bf16(kRes, 128, false, true);
       constexpr uint32_t idesc_dqk = make_idesc_bf16(kRes, DQK, false, true);
-      const uint32_t r1 = smem_u32(sR1), r2 = smem_u32(sR2), x1 = smem_u32(sX1), x2 = smem_u32(sX2);
+      // K-major views (T GEMMs) and MN-major views (accumulating GEMMs) of the tiles; later K-steps and ring
+      // stages only move the start-address field.
+      const uint64_t r1d = make_smem_desc(smem_u32(sR1), 16, 1024), r2d = make_smem_desc(smem_u32(sR2), 16, 1024);
+      const uint64_t x1k = make_smem_desc(smem_u32(sX1), 16, 1024), x2k = make_smem_desc(smem_u32(sX2), 16, 1024);
+      const uint64_t x1m = make_smem_desc(smem_u32(sX1), kStr * 128, 1024);
+      const uint64_t x2m = make_smem_desc(smem_u32(sX2), kStr * 128, 1024);
       mbar_wait(res_full, 0, ctl, 0x200);
       auto issue_t = [&](int k) {
         const int s = k % NST, b = k % NBUF;
         mbar_wait(&x_full[s], (k / NST) & 1, ctl, 0x300 + s);
         tc_fence_after_sync();
         const uint32_t t1 = tmem_base + b * 128, t2 = t1 + 64;
+        const uint64_t x1s = desc_advance(x1k, s * C::kX1), x2s = desc_advance(x2k, s * C::kX2);
 #pragma unroll
         for (int kk = 0; kk < DQK / 16; ++kk) {
           const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-          umma_ss(t1, make_smem_desc(r1 + sub * (kRes * 128) + off, 16, 1024),
-                  make_smem_desc(x1 + s * C::kX1 + sub * (kStr * 128) + off, 16, 1024), idesc_t, kk > 0 ? 1u : 0u);
+          umma_ss(t1, desc_advance(r1d, sub * (kRes * 128) + off), desc_advance(x1s, sub * (kStr * 128) + off), idesc_t,
+                  kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-          umma_ss(t2, make_smem_desc(r2 + sub * (kRes * 128) + off, 16, 1024),
-                  make_smem_desc(x2 + s * C::kX2 + sub * (kStr * 128) + off, 16, 1024), idesc_t, kk > 0 ? 1u : 0u);
+          umma_ss(t2, desc_advance(r2d, sub * (kRes * 128) + off), desc_advance(x2s, sub * (kStr * 128) + off), idesc_t,
+                  kk > 0 ? 1u : 0u);
         }
         umma_commit(&t_full[k & 1]);
       };
@@ -228,20 +238,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         tc_fence_after_sync();
         const uint32_t a1 = tmem_base + b * 128, a2 = a1 + 64;
         const uint32_t acc = k > 0 ? 1u : 0u;
+        const uint64_t x1s = desc_advance(x1m, s * C::kX1), x2s = desc_advance(x2m, s * C::kX2);
         if constexpr (MODE == kDkDv) {
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dV += P^T dO_i
-            umma_ts(tmem_base + C::kAccCol, a1 + kk * 8,
-                    make_smem_desc(x2 + s * C::kX2 + kk * 2048, kStr * 128, 1024), idesc_dv, acc | (kk > 0 ? 1u : 0u));
+            umma_ts(tmem_base + C::kAccCol, a1 + kk * 8, desc_advance(x2s, kk * 2048), idesc_dv, acc | (kk > 0 ? 1u : 0u));
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dK += dS^T Q_i
-            umma_ts(tmem_base + C::kAccCol + 128, a2 + kk * 8,
-                    make_smem_desc(x1 + s * C::kX1 + kk * 2048, kStr * 128, 1024), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
+            umma_ts(tmem_base + C::kAccCol + 128, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk,
+                    acc | (kk > 0 ? 1u : 0u));
         } else {
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dQ += dS K_j
-            umma_ts(tmem_base + C::kAccCol, a2 + kk * 8,
-                    make_smem_desc(x1 + s * C::kX1 + kk * 2048, kStr * 128, 1024), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
+            umma_ts(tmem_base + C::kAccCol, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
         }
         umma_commit(&x_empty[s]);
         if (NBUF == 1 && k + 1 < n_it) issue_t(k + 1);
@@ -250,6 +259,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ compute groups
+    setmaxnreg_inc<kBwdRegsHi>();
     const int w = (warp - 4) >> 2;
     const int lane_row = ((warp & 3) << 5) + lane;  // TMEM lane = row of the resident tile
     const int res_row = r0 + lane_row;              // key (kDkDv) or query (kDq) position
@@ -263,6 +273,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if (my_lse == -INFINITY) my_lse = INFINITY;
       }
     }
+    const uint64_t my_nl2 = f2_pack(-my_lse, -my_lse), my_nd2 = f2_pack(-my_delta, -my_delta);
     for (int k = w; k < n_it; k += 2) {
       const int s = k % NST, b = k % NBUF;
       const int x0 = (it_begin + k) * kStr;
@@ -276,13 +287,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tmem_ld32(t2, s2);
       tmem_ld32(t2 + 32, s2 + 32);
       tmem_wait_ld();
-      if (p.dbg != nullptr && blockIdx.x == 0 && head == 0 && batch == 0 && k == 0) {
-#pragma unroll
-        for (int i = 0; i < kStr; ++i) {
-          p.dbg[lane_row * 64 + i] = __uint_as_float(s1[i]);
-          p.dbg[8192 + lane_row * 64 + i] = __uint_as_float(s2[i]);
-        }
-      }
       // key n visible to query m iff n <= m + off
       bool need_mask;
       int lim;  // kDkDv: first visible column (query) index; kDq: last visible column (key) index
@@ -293,21 +297,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         need_mask = p.causal && (x0 + kStr - 1 > r0 + p.causal_off);
         lim = res_row + p.causal_off - x0;  // column i visible iff i <= lim
       }
-      const float* st_l = sStat + (s * 2 + 0) * kStr;
-      const float* st_d = sStat + (s * 2 + 1) * kStr;
+      const uint64_t* st_l = reinterpret_cast<const uint64_t*>(sStat + (s * 2 + 0) * kStr);  // pairs of -lse
+      const uint64_t* st_d = reinterpret_cast<const uint64_t*>(sStat + (s * 2 + 1) * kStr);  // pairs of -delta
+      const uint64_t c2 = f2_pack(c, c);
       uint32_t pa[kStr / 2], da[kStr / 2];
 #pragma unroll
       for (int i = 0; i < kStr; i += 2) {
-        float l0, l1, d0, d1;
+        uint64_t nl2, nd2;
         if constexpr (MODE == kDkDv) {
-          const float2 lv = *reinterpret_cast<const float2*>(st_l + i);
-          const float2 dv = *reinterpret_cast<const float2*>(st_d + i);
-          l0 = lv.x; l1 = lv.y; d0 = dv.x; d1 = dv.y;
+          nl2 = st_l[i >> 1];
+          nd2 = st_d[i >> 1];
         } else {
-          l0 = l1 = my_lse; d0 = d1 = my_delta;
+          nl2 = my_nl2;
+          nd2 = my_nd2;
         }
-        float p0 = fast_exp2(fmaf(__uint_as_float(s1[i]), c, -l0));
-        float p1 = fast_exp2(fmaf(__uint_as_float(s1[i + 1]), c, -l1));
+        float x0, x1;
+        f2_unpack(f2_fma(f2_pack(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1])), c2, nl2), x0, x1);
+        float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
         if (need_mask) {
           if constexpr (MODE == kDkDv) {
             if (i < lim) p0 = 0.f;
@@ -317,8 +323,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             if (i + 1 > lim) p1 = 0.f;
           }
         }
-        const float g0 = p0 * (__uint_as_float(s2[i]) - d0);
-        const float g1 = p1 * (__uint_as_float(s2[i + 1]) - d1);
+        float g0, g1;
+        f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1])), nd2)), g0, g1);
         pa[i >> 1] = pack_bf16(p0, p1);
         da[i >> 1] = pack_bf16(g0, g1);
       }
@@ -385,6 +391,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
       }
     }
+  }
+
+  else {
+    setmaxnreg_dec<kBwdRegsLo>();  // warps 2 and 3 only give their registers away
   }
 
   // ------------------------------------------------------------------ teardown

@@ -21,6 +21,14 @@
 #include "common.cuh"
 #include "host_common.h"
 
+#ifndef PITH_FWD_REGS_LO
+#define PITH_FWD_REGS_LO 64
+#define PITH_FWD_REGS_HI 216
+#endif
+#ifndef PITH_PACKED_F32
+#define PITH_PACKED_F32 1  // scale / sum the scores with fma.f32x2 / add.f32x2 (two floats per instruction)
+#endif
+
 namespace pith {
 
 struct FwdParams {
@@ -57,26 +65,24 @@ struct FwdSmem {
 };
 
 // S[128 x BN] = Q_tile[128 x DQK] * K_blk[BN x DQK]^T, both operands K-major in shared memory.
+// qdesc / kdesc describe the first [rows][64] sub-tile; later K-steps only move the start address.
 template <int DQK, int BN>
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t sq, uint32_t sk, uint32_t idesc) {
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t qdesc, uint64_t kdesc, uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < DQK / 16; ++kk) {
     const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-    const uint64_t a = make_smem_desc(sq + sub * (kBM * 128) + off, 16, 1024);
-    const uint64_t b = make_smem_desc(sk + sub * (BN * 128) + off, 16, 1024);
-    umma_ss(d_tmem, a, b, idesc, kk > 0 ? 1u : 0u);
+    umma_ss(d_tmem, desc_advance(qdesc, sub * (kBM * 128) + off), desc_advance(kdesc, sub * (BN * 128) + off), idesc,
+            kk > 0 ? 1u : 0u);
   }
 }
 
 // O[128 x 128] (+)= P[128 x BN] (bf16 in TMEM) * V_blk[BN x 128] (MN-major in shared memory:
 // two [BN][64] column blocks, BN * 128 bytes apart).
 template <int BN>
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t sv, uint32_t idesc, bool acc) {
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint64_t vdesc, uint32_t idesc, bool acc) {
 #pragma unroll
-  for (int kk = 0; kk < BN / 16; ++kk) {
-    const uint64_t b = make_smem_desc(sv + kk * 2048, BN * 128, 1024);
-    umma_ts(d_tmem, p_tmem + kk * 8, b, idesc, (acc || kk > 0) ? 1u : 0u);
-  }
+  for (int kk = 0; kk < BN / 16; ++kk)
+    umma_ts(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
 }
 
 template <int DQK, int BN, int KST, int VST>
@@ -142,8 +148,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Register budget: the four warps of warpgroup 0 (producer, MMA issuer, two idle) need few registers,
+  // the softmax groups hold a whole 128-column score row each.
+  // (each role branch below starts with its own setmaxnreg so that the limit holds for exactly that code)
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    setmaxnreg_dec<PITH_FWD_REGS_LO>();
     if (lane == 0 && nmax > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
@@ -170,17 +180,24 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    setmaxnreg_dec<PITH_FWD_REGS_LO>();
     if (lane == 0 && nmax > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(kBM, BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, kDV, false, true);
-      const uint32_t sq = smem_u32(sQ), sk = smem_u32(sK), sv = smem_u32(sV);
+      uint64_t qd[2], kd[KST], vd[VST];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) qd[t] = make_smem_desc(smem_u32(sQ) + t * L::kQTile, 16, 1024);
+#pragma unroll
+      for (int i = 0; i < KST; ++i) kd[i] = make_smem_desc(smem_u32(sK) + i * L::kKTile, 16, 1024);
+#pragma unroll
+      for (int i = 0; i < VST; ++i) vd[i] = make_smem_desc(smem_u32(sV) + i * L::kVTile, BN * 128, 1024);
       mbar_wait(q_full, 0, ctl, 0x300);
       mbar_wait(&k_full[0], 0, ctl, 0x400);
       tc_fence_after_sync();
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (nblk[t] > 0) {
-          issue_qk<DQK, BN>(tmem_base + t * 128, sq + t * L::kQTile, sk, idesc_qk);
+          issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[0], idesc_qk);
           umma_commit(&s_full[t]);
         }
       }
@@ -196,9 +213,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           if (j < nblk[t]) {
             mbar_wait(&p_full[t], j & 1, ctl, 0x600 + t);
             tc_fence_after_sync();
-            issue_pv<BN>(tmem_base + 256 + t * 128, tmem_base + t * 128, sv + vs * L::kVTile, idesc_pv, j > 0);
+            issue_pv<BN>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0);
             if (j + 1 < nblk[t]) {
-              issue_qk<DQK, BN>(tmem_base + t * 128, sq + t * L::kQTile, sk + ks * L::kKTile, idesc_qk);
+              issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk);
               umma_commit(&s_full[t]);
             } else {
               umma_commit(&o_full[t]);
@@ -211,6 +228,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax + epilogue
+    setmaxnreg_inc<PITH_FWD_REGS_HI>();
     const int t = (warp - 4) >> 2;                 // query tile of this warpgroup
     const int row_in_tile = ((warp & 3) << 5) + lane;  // TMEM lane == query row
     const int row = m0 + t * kBM + row_in_tile;    // query position inside this call's Q block
@@ -219,7 +237,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
     const float c = p.scale_log2;
     const int nb = nblk[t];
-    const bool dump = p.dbg != nullptr && blockIdx.x == gridDim.x - 1 && head == 0 && batch == 0 && t == 0;
 
     float m_used = -INFINITY;
     float l = 0.f;
@@ -230,10 +247,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
       for (int cchunk = 0; cchunk < BN / 32; ++cchunk) tmem_ld32(tS + cchunk * 32, sr + cchunk * 32);
       tmem_wait_ld();
-      if (dump && j == 0) {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) p.dbg[row_in_tile * 128 + i] = __uint_as_float(sr[i]);
-      }
       const int n0 = j * BN;
       const bool need_mask = (p.causal && (n0 + BN - 1 > m0 + t * kBM + p.causal_off)) || (n0 + BN > p.Sk);
       if (need_mask) {
@@ -242,9 +255,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         for (int i = 0; i < BN; ++i)
           if (n0 + i > limit) sr[i] = 0xFF800000u;  // -inf
       }
-      float m_blk = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
 #pragma unroll
-      for (int i = 0; i < BN; ++i) m_blk = fmaxf(m_blk, __uint_as_float(sr[i]));
+      for (int i = 0; i < BN; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          mx[u] = fmax3(mx[u], __uint_as_float(sr[i + 2 * u]), __uint_as_float(sr[i + 2 * u + 1]));
+      }
+      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const float m_new = fmaxf(m_used, m_blk);
       if (j == 0) {
         m_used = m_new;
@@ -266,7 +284,30 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         }
       }
       const float mc = (m_used == -INFINITY) ? 0.f : m_used * c;
-      float lsum = 0.f;
+#if PITH_PACKED_F32
+      const uint64_t c2 = f2_pack(c, c), nmc2 = f2_pack(-mc, -mc);
+      uint64_t ls2[2] = {0ull, 0ull};  // four independent partial sums, packed in pairs
+#pragma unroll
+      for (int cchunk = 0; cchunk < BN / 64; ++cchunk) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sr[cchunk * 64 + 2 * i]),
+                                             __uint_as_float(sr[cchunk * 64 + 2 * i + 1])), c2, nmc2);
+          float x0, x1;
+          f2_unpack(x2, x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          ls2[i & 1] = f2_add(ls2[i & 1], f2_pack(p0, p1));
+          pk[i] = pack_bf16(p0, p1);
+        }
+        tmem_st32(tS + cchunk * 32, pk);
+      }
+      float la, lb, lc, ld;
+      f2_unpack(ls2[0], la, lb);
+      f2_unpack(ls2[1], lc, ld);
+      const float lsum = (la + lb) + (lc + ld);
+#else
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};  // independent partial sums
 #pragma unroll
       for (int cchunk = 0; cchunk < BN / 64; ++cchunk) {
         uint32_t pk[32];
@@ -274,15 +315,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         for (int i = 0; i < 32; ++i) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cchunk * 64 + 2 * i]), c, -mc));
           const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cchunk * 64 + 2 * i + 1]), c, -mc));
-          lsum += p0 + p1;
+          ls[(2 * i) & 3] += p0;
+          ls[(2 * i + 1) & 3] += p1;
           pk[i] = pack_bf16(p0, p1);
-          if (dump && j == 0) {
-            p.dbg[16384 + row_in_tile * 128 + cchunk * 64 + 2 * i] = p0;
-            p.dbg[16384 + row_in_tile * 128 + cchunk * 64 + 2 * i + 1] = p1;
-          }
         }
         tmem_st32(tS + cchunk * 32, pk);
       }
+      const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+#endif
       l += lsum;
       tmem_wait_st();
       tc_fence_before_sync();
@@ -297,10 +337,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const bool row_ok = row < p.Sq;
     float inv = (l > 0.f) ? 1.0f / l : 0.f;
     float lse2 = (l > 0.f) ? fmaf(m_used, c, fast_log2(l)) : -INFINITY;
-    if (dump) {
-      p.dbg[3 * 16384 + 2 * row_in_tile] = m_used;
-      p.dbg[3 * 16384 + 2 * row_in_tile + 1] = l;
-    }
     float w_prev = 0.f;
     if (p.prev_o != nullptr) {
       const float pl = row_ok ? p.prev_lse[batch * p.pls[0] + head * p.pls[1] + row] : -INFINITY;
@@ -325,10 +361,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) orr[i] = 0u;
-      }
-      if (dump) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) p.dbg[2 * 16384 + row_in_tile * 128 + cchunk * 32 + i] = __uint_as_float(orr[i]);
       }
       if (row_ok) {
         float ov[32];
@@ -358,6 +390,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         }
       }
     }
+  }
+
+  else {
+    setmaxnreg_dec<PITH_FWD_REGS_LO>();  // warps 2 and 3 only give their registers away
   }
 
   // ------------------------------------------------------------------ teardown

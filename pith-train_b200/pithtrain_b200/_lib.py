@@ -9,7 +9,10 @@ import ctypes
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libpith_b200.so"
+import os
+
+# PITH_B200_LIB overrides the library location (used to compare builds); the default is the in-tree build.
+LIB_PATH = Path(os.environ.get("PITH_B200_LIB", Path(__file__).resolve().parent / "libpith_b200.so"))
 
 I64x3 = c_int64 * 3
 I64x2 = c_int64 * 2

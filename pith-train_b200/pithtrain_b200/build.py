@@ -18,7 +18,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC_DIR = PKG_DIR.parent / "csrc"
 INCLUDE_DIR = PKG_DIR.parent.parent / "include"
 BUILD_DIR = CSRC_DIR / "build"
-LIB_PATH = PKG_DIR / "libpith_b200.so"
+LIB_PATH = Path(os.environ.get("PITH_B200_LIB", PKG_DIR / "libpith_b200.so"))
 
 SOURCES = ["host_common.cu", "elementwise.cu", "attn_fwd.cu", "attn_bwd.cu", "noalloc.cu"]
 
@@ -28,6 +28,11 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]
+
+
+def _extra_flags() -> list[str]:
+    """Extra nvcc flags from PITH_B200_NVCC_FLAGS (e.g. -DPITH_PACKED_F32=1), for experiments."""
+    return os.environ.get("PITH_B200_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:
@@ -48,7 +53,7 @@ def _fingerprint() -> str:
     for f in files:
         h.update(f.name.encode())
         h.update(f.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()
 
 
@@ -67,7 +72,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(src: Path) -> Path:
         obj = BUILD_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(INCLUDE_DIR), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *_extra_flags(), *extra, "-I", str(INCLUDE_DIR), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode != 0:
             sys.stderr.write(f"$ {' '.join(cmd)}\n{r.stdout}{r.stderr}\n")
