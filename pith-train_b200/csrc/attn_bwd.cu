@@ -1,4 +1,5 @@
-// Attention backward for sm_100a. One kernel template, two modes, both built from the same
+// Attention backward for sm_100a, generic variant (used for the MLA head dimensions 192 / 128; head
+// dimension 128 takes the wider-tile kernel in attn_bwd128.cu). One kernel template, two modes, both built from the same
 // pipeline: a 128-row tile stays resident in shared memory, 64-row tiles stream past it through
 // a TMA ring, tcgen05 MMAs produce two [128 x 64] fp32 tiles in TMEM, two warpgroups turn them
 // into bf16 operands (written back into TMEM) and a second round of MMAs accumulates the result.
@@ -25,26 +26,10 @@
 // A1 / A2 (packed bf16) overlay the first 32 columns of T1 / T2. Accumulators follow the buffers.
 #include "../../include/pith_b200.h"
 #include "common.cuh"
+#include "attn_bwd_common.h"
 #include "host_common.h"
 
 namespace pith {
-
-enum BwdMode : int { kDkDv = 0, kDq = 1 };
-
-struct BwdParams {
-  const float* lse;
-  const float* delta;
-  float* dq_acc;
-  float* dk_acc;
-  float* dv_acc;
-  float* dbg;
-  uint32_t* status;
-  int B, Sq, Sk, Hq, Hkv;
-  int causal, causal_off;
-  float scale_log2, scale;
-  int64_t dqs[3], dks[3], dvs[3];
-  int64_t ls[2], dls[2];
-};
 
 constexpr int kBwdThreads = 384;
 constexpr int kBwdRegsLo = 72;   // producer / MMA-issuer warpgroup
@@ -475,9 +460,9 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->Dqk == 128) {
     if (want_dkv)
-      if (int rc = launch_bwd<128, kDkDv>(a, p, st)) return rc;
+      if (int rc = launch_bwd_d128(a, p, kDkDv, st)) return rc;
     if (want_dq)
-      if (int rc = launch_bwd<128, kDq>(a, p, st)) return rc;
+      if (int rc = launch_bwd_d128(a, p, kDq, st)) return rc;
     return kOk;
   }
   if (want_dkv)

@@ -1,0 +1,468 @@
+// Attention backward for head dimension 128 (GQA / MHA) on sm_100a.
+//
+// A tcgen05 MMA with M = 128 costs the same 64 cycles per K-step of 16 whether it is 128, 64 or 32
+// columns wide, so every GEMM here is 128 x 128: a 128-row tile is resident for the whole CTA and
+// 128-row tiles stream past it. TMEM then has room for exactly one pair of score tiles next to the
+// accumulators, so instead of double-buffering the scores the four GEMMs of an iteration are
+// interleaved with the next iteration's so that the tensor core always has a GEMM to run while the
+// 256 compute threads are in the exponentials:
+//
+//   mode kDkDv (resident K_n, V_n; streamed Q_i, dO_i; lane = key, column = query)
+//     MMA order   S^T(0) dP^T(0) | dV(0) S^T(1) dK(0) dP^T(1) | dV(1) S^T(2) dK(1) dP^T(2) | ...
+//     compute     P^T(k) = exp2(S^T c - lse) after S^T(k)      -> bf16 into T1, feeds dV(k) = P^T dO_i
+//                 dS^T(k) = P^T (dP^T - delta) after dP^T(k)   -> bf16 into T2, feeds dK(k) = dS^T Q_i
+//   mode kDq (resident Q_m, dO_m; streamed K_j, V_j; lane = query, column = key)
+//     MMA order   S(0) dP(0) | S(1) dQ(0) dP(1) | S(2) dQ(1) dP(2) | ...
+//     compute     P(k) after S(k) (kept in registers), dS(k) after dP(k) -> bf16 into T2, feeds dQ(k) = dS K_j
+//
+// lse is the log2-domain LSE of the complete softmax row, delta = rowsum(O dO). Results are scaled
+// (dK, dQ by softmax_scale) and ADDED to fp32 accumulators with vector atomics.
+//
+// Warps (384 threads): 0 = TMA producer (+ per-query statistics of the streamed tile in kDkDv), 1 = MMA
+// issuer, 4..11 = compute: thread (warp & 3, lane) owns TMEM lane = row of the resident tile, warps 4..7
+// take score columns 0..63 and warps 8..11 columns 64..127.
+// TMEM columns: T1 [0,128), T2 [128,256), accumulators [256,384) (dV or dQ) and [384,512) (dK).
+// The packed bf16 operands overlay the first half of each thread's own 64 score columns:
+// queries/keys 0..63 at columns [0,32), 64..127 at [64,96) of T1 (P^T) / T2 (dS).
+#include "attn_bwd_common.h"
+#include "common.cuh"
+#include "host_common.h"
+
+namespace pith {
+namespace bwd128 {
+
+constexpr int kThreads = 384;
+constexpr int kRegsLo = 72;
+constexpr int kRegsHi = 208;
+constexpr int kT = 128;             // tile edge (rows of both tiles, head dimension)
+constexpr int kTile = kT * kT * 2;  // bytes of one bf16 tile
+constexpr int kNST = 2;
+
+struct Smem {
+  static constexpr int kR1Off = 0;
+  static constexpr int kR2Off = kR1Off + kTile;
+  static constexpr int kX1Off = kR2Off + kTile;
+  static constexpr int kX2Off = kX1Off + kNST * kTile;
+  static constexpr int kStatOff = kX2Off + kNST * kTile;  // [kNST][2][128] floats
+  static constexpr int kBarOff = kStatOff + kNST * 2 * kT * 4;
+  static constexpr int kNumBars = 1 + 2 * kNST + 5;
+  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+  static constexpr int kAlloc = kTotal + 1024;
+};
+static_assert(Smem::kAlloc <= 232448, "shared memory budget");
+
+constexpr uint32_t kColT1 = 0, kColT2 = 128, kColAcc = 256, kColAcc2 = 384;
+
+// D[128 x 128] = A[128 x 128] * B[128 x 128]^T, both K-major in shared memory (two [128][64] sub-tiles each).
+__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < kT / 16; ++kk) {
+    const uint32_t off = (kk >> 2) * (kT * 128) + (kk & 3) * 32;
+    umma_ss(d_tmem, desc_advance(adesc, off), desc_advance(bdesc, off), idesc, kk > 0 ? 1u : 0u);
+  }
+}
+// D[128 x 128] (+)= A[128 x 128] (packed bf16 in TMEM, halves at columns +0 and +64) * B (MN-major tile in shared memory)
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc) {
+#pragma unroll
+  for (int kk = 0; kk < kT / 16; ++kk) {
+    const uint32_t a = a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+    umma_ts(d_tmem, a, desc_advance(bdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+    attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
+                       const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
+                       const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sR1 = smem + Smem::kR1Off;
+  uint8_t* sR2 = smem + Smem::kR2Off;
+  uint8_t* sX1 = smem + Smem::kX1Off;
+  uint8_t* sX2 = smem + Smem::kX2Off;
+  float* sStat = reinterpret_cast<float*>(smem + Smem::kStatOff);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBarOff);
+  uint64_t* res_full = bars;
+  uint64_t* x_full = bars + 1;
+  uint64_t* x_empty = x_full + kNST;
+  uint64_t* t1_full = x_empty + kNST;
+  uint64_t* t2_full = t1_full + 1;
+  uint64_t* p_full = t2_full + 1;   // kDkDv: P^T is in TMEM; kDq: T1 has been read
+  uint64_t* ds_full = p_full + 1;   // dS is in TMEM
+  uint64_t* acc_full = ds_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const AbortCtl ctl{p.status, abort_flag};
+
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.Hq / p.Hkv);
+  int r0, it_begin, it_end;
+  if constexpr (MODE == kDkDv) {
+    r0 = blockIdx.x * kT;  // first key; small r0 = most work, launched first
+    it_begin = p.causal ? max(0, r0 - p.causal_off) / kT : 0;
+    it_end = (p.Sq + kT - 1) / kT;
+  } else {
+    r0 = (gridDim.x - 1 - blockIdx.x) * kT;  // first query; late queries first
+    it_begin = 0;
+    it_end = (p.Sk + kT - 1) / kT;
+    if (p.causal) {
+      const int last_key = min(r0 + kT - 1, p.Sq - 1) + p.causal_off;
+      it_end = last_key < 0 ? 0 : min(it_end, last_key / kT + 1);
+    }
+  }
+  const int n_it = max(0, it_end - it_begin);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0u;
+    mbar_init(res_full, 1);
+    for (int i = 0; i < kNST; ++i) {
+      mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
+      mbar_init(&x_empty[i], 1);
+    }
+    mbar_init(t1_full, 1);
+    mbar_init(t2_full, 1);
+    mbar_init(p_full, 256);
+    mbar_init(ds_full, 256);
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int r1_head = (MODE == kDkDv) ? kv_head : head;  // head index of the resident tensors
+  const int x_head = (MODE == kDkDv) ? head : kv_head;   // head index of the streamed tensors
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    setmaxnreg_dec<kRegsLo>();
+    if (n_it > 0) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tm_r1);
+        tma_prefetch_desc(&tm_r2);
+        tma_prefetch_desc(&tm_x1);
+        tma_prefetch_desc(&tm_x2);
+        mbar_arrive_expect_tx(res_full, 2 * kTile);
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+          tma_load_4d(sR1 + sub * (kT * 128), &tm_r1, res_full, sub * 64, r1_head, r0, batch);
+          tma_load_4d(sR2 + sub * (kT * 128), &tm_r2, res_full, sub * 64, r1_head, r0, batch);
+        }
+      }
+      for (int k = 0; k < n_it; ++k) {
+        const int s = k % kNST;
+        const int x0 = (it_begin + k) * kT;
+        // Statistics of the 128 streamed queries (-lse, -inf where the row does not exist or saw no key; -delta),
+        // fetched before the stage is waited for so that the load latency hides behind the wait.
+        float nl[4], nd[4];
+        if constexpr (MODE == kDkDv) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int m = x0 + j * 32 + lane;
+            nl[j] = -INFINITY;
+            nd[j] = 0.f;
+            if (m < p.Sq) {
+              const float l = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
+              nl[j] = (l == -INFINITY) ? -INFINITY : -l;
+              nd[j] = -p.delta[batch * p.dls[0] + head * p.dls[1] + m];
+            }
+          }
+        }
+        if (lane == 0) mbar_wait(&x_empty[s], ((k / kNST) & 1) ^ 1, ctl, 0x100 + s);
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&x_full[s], 2 * kTile);
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            tma_load_4d(sX1 + s * kTile + sub * (kT * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
+            tma_load_4d(sX2 + s * kTile + sub * (kT * 128), &tm_x2, &x_full[s], sub * 64, x_head, x0, batch);
+          }
+        }
+        if constexpr (MODE == kDkDv) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            sStat[(s * 2 + 0) * kT + j * 32 + lane] = nl[j];
+            sStat[(s * 2 + 1) * kT + j * 32 + lane] = nd[j];
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&x_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    setmaxnreg_dec<kRegsLo>();
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(kT, kT, false, false);  // both operands K-major
+      constexpr uint32_t idesc_mn = make_idesc_bf16(kT, kT, false, true);   // B operand MN-major
+      const uint64_t r1d = make_smem_desc(smem_u32(sR1), 16, 1024), r2d = make_smem_desc(smem_u32(sR2), 16, 1024);
+      uint64_t x1k[kNST], x2k[kNST], x1m[kNST], x2m[kNST];
+#pragma unroll
+      for (int s = 0; s < kNST; ++s) {
+        x1k[s] = make_smem_desc(smem_u32(sX1) + s * kTile, 16, 1024);
+        x2k[s] = make_smem_desc(smem_u32(sX2) + s * kTile, 16, 1024);
+        x1m[s] = make_smem_desc(smem_u32(sX1) + s * kTile, kT * 128, 1024);
+        x2m[s] = make_smem_desc(smem_u32(sX2) + s * kTile, kT * 128, 1024);
+      }
+      const uint32_t t1 = tmem_base + kColT1, t2 = tmem_base + kColT2;
+      mbar_wait(res_full, 0, ctl, 0x200);
+      mbar_wait(&x_full[0], 0, ctl, 0x300);
+      tc_fence_after_sync();
+      gemm_ss(t1, r1d, x1k[0], idesc_kk);
+      umma_commit(t1_full);
+      gemm_ss(t2, r2d, x2k[0], idesc_kk);
+      umma_commit(t2_full);
+      for (int k = 0; k < n_it; ++k) {
+        const int s = k & 1, sn = s ^ 1;
+        const bool more = k + 1 < n_it;
+        if constexpr (MODE == kDkDv) {
+          mbar_wait(p_full, k & 1, ctl, 0x400);
+          tc_fence_after_sync();
+          gemm_ts(tmem_base + kColAcc, t1, s ? x2m[1] : x2m[0], idesc_mn, k > 0);  // dV += P^T dO_i
+          if (more) {
+            mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
+            tc_fence_after_sync();
+            gemm_ss(t1, r1d, sn ? x1k[1] : x1k[0], idesc_kk);  // S^T(k+1)
+            umma_commit(t1_full);
+          }
+          mbar_wait(ds_full, k & 1, ctl, 0x500);
+          tc_fence_after_sync();
+          gemm_ts(tmem_base + kColAcc2, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0);  // dK += dS^T Q_i
+          umma_commit(&x_empty[s]);
+          if (more) {
+            gemm_ss(t2, r2d, sn ? x2k[1] : x2k[0], idesc_kk);  // dP^T(k+1)
+            umma_commit(t2_full);
+          }
+        } else {
+          if (more) {
+            mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
+            mbar_wait(p_full, k & 1, ctl, 0x400);  // T1 of iteration k has been read
+            tc_fence_after_sync();
+            gemm_ss(t1, r1d, sn ? x1k[1] : x1k[0], idesc_kk);  // S(k+1)
+            umma_commit(t1_full);
+          }
+          mbar_wait(ds_full, k & 1, ctl, 0x500);
+          tc_fence_after_sync();
+          gemm_ts(tmem_base + kColAcc, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0);  // dQ += dS K_j
+          umma_commit(&x_empty[s]);
+          if (more) {
+            gemm_ss(t2, r2d, sn ? x2k[1] : x2k[0], idesc_kk);  // dP(k+1)
+            umma_commit(t2_full);
+          }
+        }
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ compute
+    setmaxnreg_inc<kRegsHi>();
+    const int h = (warp - 4) >> 2;                  // column half
+    const int lane_row = ((warp & 3) << 5) + lane;  // TMEM lane = row of the resident tile
+    const int res_row = r0 + lane_row;              // key (kDkDv) or query (kDq) position
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
+    const uint32_t t1 = tmem_base + lane_addr + kColT1 + h * 64, t2 = tmem_base + lane_addr + kColT2 + h * 64;
+    const float c = p.scale_log2;
+    const uint64_t c2 = f2_pack(c, c);
+    float my_lse = INFINITY, my_delta = 0.f;
+    if constexpr (MODE == kDq) {
+      if (res_row < p.Sq && n_it > 0) {
+        my_lse = p.lse[batch * p.ls[0] + head * p.ls[1] + res_row];
+        my_delta = p.delta[batch * p.dls[0] + head * p.dls[1] + res_row];
+        if (my_lse == -INFINITY) my_lse = INFINITY;
+      }
+    }
+    const uint64_t my_nl2 = f2_pack(-my_lse, -my_lse), my_nd2 = f2_pack(-my_delta, -my_delta);
+    for (int k = 0; k < n_it; ++k) {
+      const int s = k & 1;
+      const int x0 = (it_begin + k) * kT + h * 64;  // global position of this thread's first column
+      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k >> 1) & 1, ctl, 0x600 + s);
+      const ulonglong2* st_l = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 0) * kT + h * 64);
+      const ulonglong2* st_d = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 1) * kT + h * 64);
+      // key n visible to query m iff n <= m + off
+      bool need_mask;
+      int lim;  // kDkDv: first visible column; kDq: last visible column (relative to this thread's 64)
+      if constexpr (MODE == kDkDv) {
+        need_mask = p.causal && (r0 + kT - 1 > x0 + p.causal_off);
+        lim = res_row - p.causal_off - x0;
+      } else {
+        need_mask = p.causal && (x0 + 63 > r0 + p.causal_off);
+        lim = res_row + p.causal_off - x0;
+      }
+      // ---- P = exp2(S c - lse)
+      mbar_wait(t1_full, k & 1, ctl, 0x700);
+      tc_fence_after_sync();
+      uint32_t pv[64];  // scores, then probabilities (fp32 bit patterns)
+      tmem_ld32(t1, pv);
+      tmem_ld32(t1 + 32, pv + 32);
+      tmem_wait_ld();
+      if constexpr (MODE == kDq) {  // nothing is written back into T1: the next S may overwrite it right away
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+      }
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        uint64_t nl2[2];
+        if constexpr (MODE == kDkDv) {
+          const ulonglong2 lv = st_l[i >> 2];
+          nl2[0] = lv.x; nl2[1] = lv.y;
+        } else {
+          nl2[0] = nl2[1] = my_nl2;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int j = i + 2 * u;
+          float a0, a1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(pv[j]), __uint_as_float(pv[j + 1])), c2, nl2[u]), a0, a1);
+          float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+          if (need_mask) {
+            if constexpr (MODE == kDkDv) {
+              if (j < lim) p0 = 0.f;
+              if (j + 1 < lim) p1 = 0.f;
+            } else {
+              if (j > lim) p0 = 0.f;
+              if (j + 1 > lim) p1 = 0.f;
+            }
+          }
+          pv[j] = __float_as_uint(p0);
+          pv[j + 1] = __float_as_uint(p1);
+        }
+      }
+      if constexpr (MODE == kDkDv) {
+        uint32_t pa[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pa[i] = pack_bf16(__uint_as_float(pv[2 * i]), __uint_as_float(pv[2 * i + 1]));
+        tmem_st32(t1, pa);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(p_full);
+      }
+      // ---- dS = P (dP - delta)
+      mbar_wait(t2_full, k & 1, ctl, 0x800);
+      tc_fence_after_sync();
+      uint32_t dp[64];
+      tmem_ld32(t2, dp);
+      tmem_ld32(t2 + 32, dp + 32);
+      tmem_wait_ld();
+      uint32_t da[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        uint64_t nd2[2];
+        if constexpr (MODE == kDkDv) {
+          const ulonglong2 dv = st_d[i >> 2];
+          nd2[0] = dv.x; nd2[1] = dv.y;
+        } else {
+          nd2[0] = nd2[1] = my_nd2;
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int j = i + 2 * u;
+          float g0, g1;
+          f2_unpack(f2_mul(f2_pack(__uint_as_float(pv[j]), __uint_as_float(pv[j + 1])),
+                           f2_add(f2_pack(__uint_as_float(dp[j]), __uint_as_float(dp[j + 1])), nd2[u])), g0, g1);
+          da[j >> 1] = pack_bf16(g0, g1);
+        }
+      }
+      tmem_st32(t2, da);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(ds_full);
+    }
+
+    // ---- write-out: accumulators -> scaled fp32 atomics
+    if (n_it > 0) {
+      mbar_wait(acc_full, 0, ctl, 0x900);
+      tc_fence_after_sync();
+      float* dst;
+      uint32_t src;
+      float scl;
+      int ncols;
+      bool ok;
+      if constexpr (MODE == kDkDv) {
+        ok = res_row < p.Sk;
+        ncols = 128;
+        if (h == 0) {
+          dst = p.dv_acc + batch * p.dvs[0] + static_cast<int64_t>(res_row) * p.dvs[1] + kv_head * p.dvs[2];
+          src = tmem_base + lane_addr + kColAcc;
+          scl = 1.0f;
+        } else {
+          dst = p.dk_acc + batch * p.dks[0] + static_cast<int64_t>(res_row) * p.dks[1] + kv_head * p.dks[2];
+          src = tmem_base + lane_addr + kColAcc2;
+          scl = p.scale;
+        }
+      } else {
+        ok = res_row < p.Sq;
+        ncols = 64;
+        dst = p.dq_acc + batch * p.dqs[0] + static_cast<int64_t>(res_row) * p.dqs[1] + head * p.dqs[2] + h * 64;
+        src = tmem_base + lane_addr + kColAcc + h * 64;
+        scl = p.scale;
+      }
+      for (int cc = 0; cc < ncols / 32; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(src + cc * 32, r);
+        tmem_wait_ld();
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            atomicAdd(reinterpret_cast<float4*>(dst + cc * 32) + i,
+                      make_float4(__uint_as_float(r[4 * i]) * scl, __uint_as_float(r[4 * i + 1]) * scl,
+                                  __uint_as_float(r[4 * i + 2]) * scl, __uint_as_float(r[4 * i + 3]) * scl));
+        }
+      }
+    }
+  } else {
+    setmaxnreg_dec<kRegsLo>();  // warps 2 and 3 only give their registers away
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    // Something gave up waiting: let copies and MMAs still in flight drain before the
+    // shared memory and TMEM of this CTA are handed back.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int MODE>
+static int launch(const pith_attn_bwd_args* a, const BwdParams& p, cudaStream_t st) {
+  CUtensorMap tq, tk, tv, tdo;
+  if (int rc = make_tensor_map(&tq, a->q, 2, a->B, a->Sq, a->Hq, a->Dqk, a->q_stride, 64, kT)) return rc;
+  if (int rc = make_tensor_map(&tdo, a->dout, 2, a->B, a->Sq, a->Hq, a->Dv, a->do_stride, 64, kT)) return rc;
+  if (int rc = make_tensor_map(&tk, a->k, 2, a->B, a->Sk, a->Hkv, a->Dqk, a->k_stride, 64, kT)) return rc;
+  if (int rc = make_tensor_map(&tv, a->v, 2, a->B, a->Sk, a->Hkv, a->Dv, a->v_stride, 64, kT)) return rc;
+  auto kern = attn_bwd128_kernel<MODE>;
+  PITH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kAlloc));
+  if (MODE == kDkDv) {
+    dim3 grid((a->Sk + kT - 1) / kT, a->Hq, a->B);
+    kern<<<grid, kThreads, Smem::kAlloc, st>>>(tk, tv, tq, tdo, p);
+  } else {
+    dim3 grid((a->Sq + kT - 1) / kT, a->Hq, a->B);
+    kern<<<grid, kThreads, Smem::kAlloc, st>>>(tq, tdo, tk, tv, p);
+  }
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace bwd128
+
+int launch_bwd_d128(const pith_attn_bwd_args* a, const BwdParams& p, int mode, cudaStream_t st) {
+  return mode == kDkDv ? bwd128::launch<kDkDv>(a, p, st) : bwd128::launch<kDq>(a, p, st);
+}
+
+}  // namespace pith

@@ -1,0 +1,30 @@
+// Shared between the two attention-backward translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pith_b200.h"
+
+namespace pith {
+
+enum BwdMode : int { kDkDv = 0, kDq = 1 };
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  float* dq_acc;
+  float* dk_acc;
+  float* dv_acc;
+  float* dbg;
+  uint32_t* status;
+  int B, Sq, Sk, Hq, Hkv;
+  int causal, causal_off;
+  float scale_log2, scale;
+  int64_t dqs[3], dks[3], dvs[3];
+  int64_t ls[2], dls[2];
+};
+
+// Head dimension 128 (GQA / MHA) with 128-wide streamed tiles (attn_bwd128.cu).
+int launch_bwd_d128(const pith_attn_bwd_args* a, const BwdParams& p, int mode, cudaStream_t st);
+
+}  // namespace pith
