@@ -58,13 +58,17 @@ struct Smem {
   static constexpr int kX2Off = kX1Off + kNST * kTile;
   static constexpr int kStatOff = kX2Off + kNST * kTile;  // [kNST][2][128] floats
   static constexpr int kBarOff = kStatOff + kNST * 2 * kT * 4;
-  static constexpr int kNumBars = 1 + 2 * kNST + 5;
+  static constexpr int kNumBars = 1 + 4 * kNST + 6;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;
 };
 static_assert(Smem::kAlloc <= 232448, "shared memory budget");
 
 constexpr uint32_t kColT1 = 0, kColT2 = 128, kColAcc = 256, kColAcc2 = 384;
+// Mode kDq leaves TMEM columns [384,512) unused: the resident Q and dO tiles are copied there once (packed bf16,
+// 64 columns each) so that S and dP take their A operand from TMEM and only the streamed tile is read from shared
+// memory; an MMA with both operands in shared memory re-reads 8 KB per K-step and competes with the TMA writes.
+constexpr uint32_t kColR1 = 384, kColR2 = 448;
 
 // D[128 x 128] = A[128 x 128] * B[128 x 128]^T, both K-major in shared memory (two [128][64] sub-tiles each).
 __device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
@@ -83,6 +87,28 @@ __device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
   }
 }
 
+// D[128 x 128] = A[128 x 128] (packed bf16 in TMEM, 64 consecutive columns) * B[128 x 128]^T (K-major in shared memory)
+__device__ __forceinline__ void gemm_tk(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < kT / 16; ++kk) {
+    const uint32_t off = (kk >> 2) * (kT * 128) + (kk & 3) * 32;
+    umma_ts(d_tmem, a_tmem + kk * 8, desc_advance(bdesc, off), idesc, kk > 0 ? 1u : 0u);
+  }
+}
+// Row `row` of a [128][128] bf16 tile (two swizzled [128][64] sub-tiles in shared memory) -> 64 packed TMEM columns.
+__device__ __forceinline__ void copy_row_to_tmem(const uint8_t* tile, int row, uint32_t taddr) {
+#pragma unroll
+  for (int sub = 0; sub < 2; ++sub) {
+    uint32_t r[32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 v = *reinterpret_cast<const uint4*>(tile + sub * (kT * 128) + row * 128 + ((c ^ (row & 7)) << 4));
+      r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+    }
+    tmem_st32(taddr + sub * 32, r);
+  }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
     attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
@@ -97,13 +123,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   float* sStat = reinterpret_cast<float*>(smem + Smem::kStatOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBarOff);
   uint64_t* res_full = bars;
-  uint64_t* x_full = bars + 1;
+  // The two streamed tiles have separate rings: X2 (dO_i / V_j) is last used earlier than X1 (Q_i / K_j), so
+  // its next load can start earlier, and the GEMM that needs X1 does not wait for X2's bytes.
+  uint64_t* x_full = bars + 1;          // X1 (+ statistics in kDkDv)
   uint64_t* x_empty = x_full + kNST;
-  uint64_t* t1_full = x_empty + kNST;
+  uint64_t* x2_full = x_empty + kNST;
+  uint64_t* x2_empty = x2_full + kNST;
+  uint64_t* t1_full = x2_empty + kNST;
   uint64_t* t2_full = t1_full + 1;
   uint64_t* p_full = t2_full + 1;   // kDkDv: P^T is in TMEM; kDq: T1 has been read
   uint64_t* ds_full = p_full + 1;   // dS is in TMEM
   uint64_t* acc_full = ds_full + 1;
+  uint64_t* rt_full = acc_full + 1;  // kDq: resident tiles are in TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -136,12 +167,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int i = 0; i < kNST; ++i) {
       mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
       mbar_init(&x_empty[i], 1);
+      mbar_init(&x2_full[i], 1);
+      mbar_init(&x2_empty[i], 1);
     }
     mbar_init(t1_full, 1);
     mbar_init(t2_full, 1);
     mbar_init(p_full, 256);
     mbar_init(ds_full, 256);
     mbar_init(acc_full, 1);
+    mbar_init(rt_full, 256);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -172,44 +206,57 @@ __global__ void __launch_bounds__(kThreads, 1)
           tma_load_4d(sR2 + sub * (kT * 128), &tm_r2, res_full, sub * 64, r1_head, r0, batch);
         }
       }
-      for (int k = 0; k < n_it; ++k) {
-        const int s = k % kNST;
-        const int x0 = (it_begin + k) * kT;
-        // Statistics of the 128 streamed queries (-lse, -inf where the row does not exist or saw no key; -delta),
-        // fetched before the stage is waited for so that the load latency hides behind the wait.
-        float nl[4], nd[4];
+      // Statistics of the streamed queries (kDkDv): raw lse / delta of iteration k are loaded two iterations ahead
+      // into registers (plain global loads take thousands of cycles next to the TMA traffic) and written to the
+      // stage as -lse (-inf where the row does not exist or saw no key) and -delta.
+      auto load_stats = [&](int k, float (&rl)[4], float (&rd)[4]) {
         if constexpr (MODE == kDkDv) {
+          const int x0 = (it_begin + k) * kT;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int m = x0 + j * 32 + lane;
-            nl[j] = -INFINITY;
-            nd[j] = 0.f;
-            if (m < p.Sq) {
-              const float l = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
-              nl[j] = (l == -INFINITY) ? -INFINITY : -l;
-              nd[j] = -p.delta[batch * p.dls[0] + head * p.dls[1] + m];
+            rl[j] = -INFINITY;
+            rd[j] = 0.f;
+            if (k < n_it && m < p.Sq) {
+              rl[j] = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
+              rd[j] = p.delta[batch * p.dls[0] + head * p.dls[1] + m];
             }
           }
         }
-        if (lane == 0) mbar_wait(&x_empty[s], ((k / kNST) & 1) ^ 1, ctl, 0x100 + s);
-        __syncwarp();
+      };
+      auto step = [&](int k, float (&rl)[4], float (&rd)[4]) {
+        const int s = k % kNST;
+        const int x0 = (it_begin + k) * kT;
         if (lane == 0) {
-          mbar_arrive_expect_tx(&x_full[s], 2 * kTile);
+          mbar_wait(&x_empty[s], ((k / kNST) & 1) ^ 1, ctl, 0x100 + s);
+          mbar_arrive_expect_tx(&x_full[s], kTile);
 #pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
+          for (int sub = 0; sub < 2; ++sub)
             tma_load_4d(sX1 + s * kTile + sub * (kT * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
-            tma_load_4d(sX2 + s * kTile + sub * (kT * 128), &tm_x2, &x_full[s], sub * 64, x_head, x0, batch);
-          }
+          mbar_wait(&x2_empty[s], ((k / kNST) & 1) ^ 1, ctl, 0x180 + s);
+          mbar_arrive_expect_tx(&x2_full[s], kTile);
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub)
+            tma_load_4d(sX2 + s * kTile + sub * (kT * 128), &tm_x2, &x2_full[s], sub * 64, x_head, x0, batch);
         }
+        __syncwarp();  // the stage is free (lane 0 saw x_empty) before anyone writes its statistics
         if constexpr (MODE == kDkDv) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            sStat[(s * 2 + 0) * kT + j * 32 + lane] = nl[j];
-            sStat[(s * 2 + 1) * kT + j * 32 + lane] = nd[j];
+            sStat[(s * 2 + 0) * kT + j * 32 + lane] = (rl[j] == -INFINITY) ? -INFINITY : -rl[j];
+            sStat[(s * 2 + 1) * kT + j * 32 + lane] = -rd[j];
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&x_full[s]);
+          load_stats(k + 2, rl, rd);  // consumed two steps from now
         }
+      };
+      float la[4], da_[4], lb[4], db[4];
+      load_stats(0, la, da_);
+      load_stats(1, lb, db);
+      for (int k = 0; k < n_it; k += 2) {
+        step(k, la, da_);
+        if (k + 1 < n_it) step(k + 1, lb, db);
       }
     }
   } else if (warp == 1) {
@@ -228,13 +275,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         x2m[s] = make_smem_desc(smem_u32(sX2) + s * kTile, kT * 128, 1024);
       }
       const uint32_t t1 = tmem_base + kColT1, t2 = tmem_base + kColT2;
-      mbar_wait(res_full, 0, ctl, 0x200);
+      if constexpr (MODE == kDq) {
+        mbar_wait(rt_full, 0, ctl, 0x210);
+      } else {
+        mbar_wait(res_full, 0, ctl, 0x200);
+      }
+      // T1 = R1 X1^T, T2 = R2 X2^T
+      auto gemm_t1 = [&](uint64_t xd) {
+        if constexpr (MODE == kDq) gemm_tk(t1, tmem_base + kColR1, xd, idesc_kk); else gemm_ss(t1, r1d, xd, idesc_kk);
+      };
+      auto gemm_t2 = [&](uint64_t xd) {
+        if constexpr (MODE == kDq) gemm_tk(t2, tmem_base + kColR2, xd, idesc_kk); else gemm_ss(t2, r2d, xd, idesc_kk);
+      };
       mbar_wait(&x_full[0], 0, ctl, 0x300);
       tc_fence_after_sync();
-      gemm_ss(t1, r1d, x1k[0], idesc_kk);
+      gemm_t1(x1k[0]);
       umma_commit(t1_full);
-      gemm_ss(t2, r2d, x2k[0], idesc_kk);
+      mbar_wait(&x2_full[0], 0, ctl, 0x380);
+      tc_fence_after_sync();
+      gemm_t2(x2k[0]);
       umma_commit(t2_full);
+      if constexpr (MODE == kDq) umma_commit(&x2_empty[0]);  // V_0 is only read by dP(0)
       PROFM_DECL;
       for (int k = 0; k < n_it; ++k) {
         const int s = k & 1, sn = s ^ 1;
@@ -244,12 +305,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           PROFM(0);
           tc_fence_after_sync();
           gemm_ts(tmem_base + kColAcc, t1, s ? x2m[1] : x2m[0], idesc_mn, k > 0);  // dV += P^T dO_i
+          umma_commit(&x2_empty[s]);  // last use of dO_i
           PROFM(1);
           if (more) {
             mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
             PROFM(2);
             tc_fence_after_sync();
-            gemm_ss(t1, r1d, sn ? x1k[1] : x1k[0], idesc_kk);  // S^T(k+1)
+            gemm_t1(sn ? x1k[1] : x1k[0]);  // S^T(k+1)
             umma_commit(t1_full);
             PROFM(3);
           }
@@ -260,7 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           umma_commit(&x_empty[s]);
           PROFM(5);
           if (more) {
-            gemm_ss(t2, r2d, sn ? x2k[1] : x2k[0], idesc_kk);  // dP^T(k+1)
+            mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
+            tc_fence_after_sync();
+            gemm_t2(sn ? x2k[1] : x2k[0]);  // dP^T(k+1)
             umma_commit(t2_full);
             PROFM(6);
           }
@@ -269,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
             mbar_wait(p_full, k & 1, ctl, 0x400);  // T1 of iteration k has been read
             tc_fence_after_sync();
-            gemm_ss(t1, r1d, sn ? x1k[1] : x1k[0], idesc_kk);  // S(k+1)
+            gemm_t1(sn ? x1k[1] : x1k[0]);  // S(k+1)
             umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
@@ -277,8 +341,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           gemm_ts(tmem_base + kColAcc, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0);  // dQ += dS K_j
           umma_commit(&x_empty[s]);
           if (more) {
-            gemm_ss(t2, r2d, sn ? x2k[1] : x2k[0], idesc_kk);  // dP(k+1)
+            mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
+            tc_fence_after_sync();
+            gemm_t2(sn ? x2k[1] : x2k[0]);  // dP(k+1)
             umma_commit(t2_full);
+            umma_commit(&x2_empty[sn]);  // V_j is only read by dP
           }
         }
       }
@@ -305,6 +372,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     const uint64_t my_nl2 = f2_pack(-my_lse, -my_lse), my_nd2 = f2_pack(-my_delta, -my_delta);
+    if constexpr (MODE == kDq) {
+      if (n_it > 0) {  // one-time copy of the resident tiles into TMEM: half 0 takes Q, half 1 takes dO
+        mbar_wait(res_full, 0, ctl, 0x220);
+        copy_row_to_tmem(h == 0 ? sR1 : sR2, lane_row, tmem_base + lane_addr + (h == 0 ? kColR1 : kColR2));
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(rt_full);
+      }
+    }
     PROFM_DECL;
     for (int k = 0; k < n_it; ++k) {
       const int s = k & 1;
@@ -322,6 +398,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         need_mask = p.causal && (x0 + 63 > r0 + p.causal_off);
         lim = res_row + p.causal_off - x0;
       }
+#ifdef PITH_SKIP_MATH  // experiment: tensor-core + TMA pipeline alone (results are garbage)
+      mbar_wait(t1_full, k & 1, ctl, 0x700);
+      PROFM(0);
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+      mbar_wait(t2_full, k & 1, ctl, 0x800);
+      PROFM(2);
+      tc_fence_before_sync();
+      mbar_arrive(ds_full);
+      (void)need_mask; (void)lim; (void)st_l; (void)st_d; (void)c2; (void)my_nl2; (void)my_nd2;
+      continue;
+#endif
       // ---- P = exp2(S c - lse)
       mbar_wait(t1_full, k & 1, ctl, 0x700);
       PROFM(0);
