@@ -103,10 +103,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       it_end = last_key < 0 ? 0 : min(it_end, last_key / kStr + 1);
     }
   }
-  const int n_it = max(0, it_end - it_begin);
+  int n_it = max(0, it_end - it_begin);
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0u;
+    // a launch that finds an error already recorded (by an earlier CTA or launch) does no work
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) ? 1u : 0u;
     mbar_init(res_full, 1);
     for (int i = 0; i < NST; ++i) {
       mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
@@ -127,6 +128,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (*abort_flag != 0u) n_it = 0;
 
   const int r1_head = (MODE == kDkDv) ? kv_head : head;  // head index of the resident tensors
   const int x_head = (MODE == kDkDv) ? head : kv_head;   // head index of the streamed tensors

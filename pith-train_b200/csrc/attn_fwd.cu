@@ -129,10 +129,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
     nblk[t] = (lo < p.Sq && kv_end > 0) ? (kv_end + BN - 1) / BN : 0;
   }
-  const int nmax = max(nblk[0], nblk[1]);
+  int nmax = max(nblk[0], nblk[1]);
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0u;
+    // a launch that finds an error already recorded (by an earlier CTA or launch) does no work
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) ? 1u : 0u;
     mbar_init(q_full, 1);
     for (int i = 0; i < KST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < VST; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
@@ -147,6 +148,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (*abort_flag != 0u) nblk[0] = nblk[1] = nmax = 0;
 
   // Register budget: the four warps of warpgroup 0 (producer, MMA issuer, two idle) need few registers,
   // the softmax groups hold a whole 128-column score row each.

@@ -66,8 +66,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Cycle budget of one wait (~1 s at 2 GHz). Checked every 32 polls.
-constexpr long long kWaitCycleLimit = 2000000000ll;
+// Cycle budget of one wait (~0.2 s at 2 GHz; a healthy wait lasts microseconds). Checked every 32 polls.
+constexpr long long kWaitCycleLimit = 400000000ll;
 
 // Waits for the phase with the given parity to complete. Returns false (after
 // recording the error and raising the CTA's abort flag) when the budget runs out
