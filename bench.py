@@ -168,6 +168,8 @@ def main():
     ap.add_argument("--sharding", choices=["zigzag", "contiguous"], default="zigzag")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="skip the comm/compute overlap measurement (N > 1)")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="issue every ring step from Python instead of replaying the ring from a CUDA graph (N > 1)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -183,7 +185,8 @@ def main():
 
     import torch.distributed as dist
     from pithtrain_b200 import build, kernels
-    from pithtrain_b200.operators.ring_attention import RingAttentionFunc, RingMLAAttentionFunc, _ring
+    from pithtrain_b200.operators.ring_attention import (RingAttentionFunc, RingMLAAttentionFunc, _ring,
+                                                         enable_cuda_graphs, release_cuda_graphs)
 
     build.build_library()
     dev = torch.device("cuda", local_rank)
@@ -192,6 +195,8 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    use_graphs = world > 1 and not args.no_graphs
+    enable_cuda_graphs(use_graphs)  # public switch of the operator: whole rings are captured once and replayed
     S1, SN, Hq, Hkv, Dqk, Dv, desc = WORKLOADS[args.workload]
     S = S1 if world == 1 else SN
     S_loc = S // world
@@ -268,8 +273,8 @@ def main():
     qd, kd, vd = q.detach(), k.detach(), v.detach()
     runs = {
         "attn_fwd_kernel": (lambda: kernels.attn_fwd(qd, kd, vd, scale, True, 0, out=out_d, lse=lse_d), 1.0),
-        "attn_bwd_kernel<kDkDv>": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, None, dk_acc, dv_acc), 2.0),
-        "attn_bwd_kernel<kDq>": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, dq_acc, None, None), 0.5),
+        "attn_bwd_kernel<kDkDv> (attn_bwd128_kernel at head_dim 128)": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, None, dk_acc, dv_acc), 2.0),
+        "attn_bwd_kernel<kDq> (attn_bwd128_kernel at head_dim 128)": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, dq_acc, None, None), 0.5),
     }
     kern = {}
     fwd_fl_local = float(Hq) * S_loc * S_loc * (Dqk + Dv)  # causal forward FLOPs of the local block
@@ -352,6 +357,7 @@ def main():
                     f"zigzag context parallel CP={world} ({S_loc} tokens per GPU)" if world > 1 and args.sharding == "zigzag"
                     else f"{args.sharding} CP={world}" if world > 1 else "single GPU (CP=1)"),
                 "sharding": args.sharding if world > 1 else "none",
+                "ring_cuda_graphs": use_graphs,
                 "l2": "inputs + gradients per step exceed the 126 MB L2 (no flush needed)",
                 "flops_convention": "fwd B*H*S^2*(Dqk+Dv), bwd 2.5x fwd",
             },
@@ -371,6 +377,7 @@ def main():
             line["overlap"] = overlap
         print(json.dumps(line), flush=True)
     if world > 1:
+        release_cuda_graphs()
         dist.barrier()
         dist.destroy_process_group()
 

@@ -4,8 +4,8 @@ The schedule is the reference's (pithtrain/operators/ring_attention/standard.py:
 :116-187 backward) with three changes made for B200:
 
 * the exchange of step ``t+1`` is issued BEFORE the attention kernel of step ``t`` and joined after
-  it, so NCCL's copy over NVLink runs under the tensor-core work instead of after it (the reference
-  waits on the requests right away, standard.py:46-50);
+  it, so NCCL's copy over NVLink (on the process group's own stream) runs under the tensor-core work
+  instead of after it (the reference waits on the requests right away, standard.py:46-50);
 * partial results are merged inside the attention kernel's epilogue into one fp32 running (O, LSE)
   instead of ~10 elementwise kernels per step (standard.py:53-66, :94);
 * the backward circulates K/V again together with a travelling fp32 dK/dV accumulator that visits
@@ -51,33 +51,21 @@ class CudaBlockBackend:
 class RingComm:
     """send-to-next / receive-from-previous over ``torch.distributed`` P2P, joined later.
 
-    On CUDA the requests are issued from a side stream ordered after the caller's stream, so the
-    transfer overlaps whatever the caller enqueues next; ``wait`` makes the caller's stream wait for
-    it. Every rank must call ``exchange`` the same number of times in the same order.
+    With NCCL the transfer runs on the process group's own communication stream: it is ordered after
+    everything already enqueued on the caller's current stream, overlaps whatever the caller enqueues
+    next, and ``wait`` makes the caller's stream wait for it. Every rank must call ``exchange`` the same
+    number of times in the same order.
     """
-
-    _streams: dict[int, "torch.cuda.Stream"] = {}
 
     def __init__(self, cp_rank: int, cp_size: int, global_ranks, device: torch.device):
         self.next_global = global_ranks[(cp_rank + 1) % cp_size]
         self.prev_global = global_ranks[(cp_rank - 1) % cp_size]
         self.device = device
-        self.stream = None
-        if device.type == "cuda":
-            idx = device.index if device.index is not None else torch.cuda.current_device()
-            if idx not in RingComm._streams:
-                RingComm._streams[idx] = torch.cuda.Stream(device=idx)
-            self.stream = RingComm._streams[idx]
 
     def exchange(self, send: torch.Tensor, recv: torch.Tensor):
         assert send.is_contiguous() and recv.is_contiguous(), "ring attention send or recv buffer is not contiguous"
-        ops = [dist.P2POp(dist.isend, send, self.next_global), dist.P2POp(dist.irecv, recv, self.prev_global)]
-        if self.stream is None:
-            return dist.batch_isend_irecv(ops)
-        self.stream.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(self.stream):
-            reqs = dist.batch_isend_irecv(ops)
-        return reqs
+        return dist.batch_isend_irecv([dist.P2POp(dist.isend, send, self.next_global),
+                                       dist.P2POp(dist.irecv, recv, self.prev_global)])
 
     @staticmethod
     def wait(reqs) -> None:
@@ -181,3 +169,105 @@ def ring_backward(backend, comm: RingComm, q, k, v, out, lse, dout, scale: float
     comm.wait(comm.exchange(last, home))
     dk_acc, dv_acc = _views(home, nk, k.shape, v.shape)
     return backend.cast(dq_acc).to(q.dtype), backend.cast(dk_acc).to(k.dtype), backend.cast(dv_acc).to(v.dtype)
+
+
+# ----------------------------------------------------------------------------- CUDA-graph replay of a whole ring
+# At high CP degrees one ring step is 100-300 us of GPU work while issuing it from Python (two exchanges, two kernel
+# launches, a memset and an add per backward step) costs about as much, so the host becomes the bottleneck. With
+# graphs enabled the complete forward (and backward) ring of one shape is captured once, NCCL exchanges included, and
+# replayed with a single launch. Opt-in, because a capture allocates static input/output buffers per shape and every
+# rank must take the same decision at the same call.
+import os as _os
+
+_graphs_enabled = _os.environ.get("PITH_B200_RING_CUDA_GRAPHS", "0") == "1"
+_graph_cache: dict = {}
+
+
+def enable_cuda_graphs(flag: bool = True) -> None:
+    """Replay ring attention from CUDA graphs (one per shape and direction). Call on every rank alike."""
+    global _graphs_enabled
+    _graphs_enabled = bool(flag)
+
+
+def cuda_graphs_enabled() -> bool:
+    return _graphs_enabled
+
+
+def release_cuda_graphs() -> None:
+    """Drops every captured graph and its buffers. Call before destroying the process group: a live graph that
+    holds NCCL work keeps the communicator busy at teardown."""
+    if _graph_cache:
+        torch.cuda.synchronize()
+        _graph_cache.clear()
+        torch.cuda.synchronize()
+
+
+class _GraphedCall:
+    """``fn(*tensors) -> tuple of tensors`` captured once on static buffers; calls copy in, replay, copy out."""
+
+    def __init__(self, fn, example_inputs):
+        self.static_in = [torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in example_inputs]
+        for s, t in zip(self.static_in, example_inputs):
+            s.copy_(t)
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):  # warm-up outside the capture (allocator, NCCL channels, function attributes)
+            for _ in range(2):
+                fn(*self.static_in)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        from ... import kernels
+        self._kernels = kernels
+        launched = kernels.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.static_out = tuple(fn(*self.static_in))
+        self.launches = kernels.launch_count - launched  # kernels of libpith_b200.so inside one replay
+
+    def __call__(self, *inputs):
+        for s, t in zip(self.static_in, inputs):
+            s.copy_(t)
+        self.graph.replay()
+        self._kernels._count(self.launches)
+        return tuple(o.clone() for o in self.static_out)
+
+
+def _use_graph(q) -> bool:
+    return _graphs_enabled and q.is_cuda and not torch.cuda.is_current_stream_capturing()
+
+
+def _key(kind, tensors, scale, cp_rank, cp_size, global_ranks, sharding):
+    return (kind, tuple((tuple(t.shape), t.dtype) for t in tensors), tensors[0].device.index, float(scale), cp_rank,
+            cp_size, tuple(global_ranks), sharding)
+
+
+def ring_forward_auto(q, k, v, scale, cp_rank, cp_size, global_ranks, sharding):
+    """ring_forward on the CUDA backend, replayed from a graph when graphs are enabled and CP > 1."""
+    backend = CudaBlockBackend()
+    comm = RingComm(cp_rank, cp_size, global_ranks, q.device)
+    if cp_size == 1 or not _use_graph(q):
+        return ring_forward(backend, comm, q, k, v, scale, cp_rank, cp_size, sharding)
+    key = _key("fwd", (q, k, v), scale, cp_rank, cp_size, global_ranks, sharding)
+    g = _graph_cache.get(key)
+    if g is None:
+        g = _GraphedCall(lambda q_, k_, v_: ring_forward(backend, comm, q_, k_, v_, scale, cp_rank, cp_size, sharding),
+                         (q, k, v))
+        _graph_cache[key] = g
+    return g(q, k, v)
+
+
+def ring_backward_auto(q, k, v, out, lse, dout, scale, cp_rank, cp_size, global_ranks, sharding):
+    """ring_backward on the CUDA backend, replayed from a graph when graphs are enabled and CP > 1."""
+    backend = CudaBlockBackend()
+    comm = RingComm(cp_rank, cp_size, global_ranks, q.device)
+    if cp_size == 1 or not _use_graph(q):
+        return ring_backward(backend, comm, q, k, v, out, lse, dout, scale, cp_rank, cp_size, sharding)
+    key = _key("bwd", (q, k, v, out, lse, dout), scale, cp_rank, cp_size, global_ranks, sharding)
+    g = _graph_cache.get(key)
+    if g is None:
+        g = _GraphedCall(lambda q_, k_, v_, o_, l_, d_: ring_backward(backend, comm, q_, k_, v_, o_, l_, d_, scale,
+                                                                     cp_rank, cp_size, sharding),
+                         (q, k, v, out, lse, dout))
+        _graph_cache[key] = g
+    return g(q, k, v, out, lse, dout)

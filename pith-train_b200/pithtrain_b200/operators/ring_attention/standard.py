@@ -55,9 +55,7 @@ class RingAttentionFunc(torch.autograd.Function):
         ctx.n_extra = len(extra)
         assert k.is_contiguous() and v.is_contiguous(), "ring attention k or v is not contiguous"
         check_sharding(sharding)
-        backend = _ring.CudaBlockBackend()
-        comm = _ring.RingComm(cp_rank, cp_size, global_ranks, q.device)
-        out, lse = _ring.ring_forward(backend, comm, q, k, v, softmax_scale, cp_rank, cp_size, sharding)
+        out, lse = _ring.ring_forward_auto(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, sharding)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.softmax_scale = softmax_scale
         ctx.cp_rank, ctx.cp_size, ctx.global_ranks, ctx.sharding = cp_rank, cp_size, global_ranks, sharding
@@ -68,10 +66,8 @@ class RingAttentionFunc(torch.autograd.Function):
         q, k, v, out, lse = ctx.saved_tensors
         if dout.stride(-1) != 1:
             dout = dout.contiguous()
-        backend = _ring.CudaBlockBackend()
-        comm = _ring.RingComm(ctx.cp_rank, ctx.cp_size, ctx.global_ranks, q.device)
-        dq, dk, dv = _ring.ring_backward(backend, comm, q, k, v, out, lse, dout, ctx.softmax_scale, ctx.cp_rank,
-                                         ctx.cp_size, ctx.sharding)
+        dq, dk, dv = _ring.ring_backward_auto(q, k, v, out, lse, dout, ctx.softmax_scale, ctx.cp_rank, ctx.cp_size,
+                                              ctx.global_ranks, ctx.sharding)
         return (dq, dk, dv, None, None, None, None) + (None,) * ctx.n_extra
 
 

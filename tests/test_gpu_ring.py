@@ -106,6 +106,19 @@ def _nccl_worker(rank, world, port, path):
             torch.cuda.synchronize()
             kernels.check_device_status(dev)
             results[tag] = [t.detach().cpu() for t in (out, ql.grad, kl.grad, vl.grad)]
+            if tag == "gqa_zigzag":
+                # the same ring replayed from CUDA graphs (captured at the first call, replayed at the second)
+                from pithtrain_b200.operators.ring_attention import enable_cuda_graphs, release_cuda_graphs
+                enable_cuda_graphs(True)
+                for _ in range(2):
+                    ql.grad = kl.grad = vl.grad = None
+                    out_g = fn(ql, kl, vl, dqk ** -0.5, group, layout)
+                    out_g.backward(dol)
+                torch.cuda.synchronize()
+                kernels.check_device_status(dev)
+                results["gqa_zigzag_graph"] = [t.detach().cpu() for t in (out_g, ql.grad, kl.grad, vl.grad)]
+                enable_cuda_graphs(False)
+                release_cuda_graphs()
         torch.save(results, os.path.join(path, f"rank{rank}.pt"))
         dist.barrier()
     finally:
@@ -121,6 +134,7 @@ def test_ring_over_nccl(cuda_device, tmp_path):
     mp.spawn(_nccl_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     res = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
     for tag, (hq, hkv, dqk), layout in (("gqa_zigzag", (8, 2, 128), "zigzag"),
+                                        ("gqa_zigzag_graph", (8, 2, 128), "zigzag"),
                                         ("gqa_contiguous", (8, 2, 128), "contiguous"),
                                         ("mla_zigzag", (16, 16, 192), "zigzag")):
         q, k, v, do = _problem(512 * world, hq, hkv, dqk)
