@@ -168,8 +168,8 @@ def main():
     ap.add_argument("--sharding", choices=["zigzag", "contiguous"], default="zigzag")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="skip the comm/compute overlap measurement (N > 1)")
-    ap.add_argument("--no-graphs", action="store_true",
-                    help="issue every ring step from Python instead of replaying the ring from a CUDA graph (N > 1)")
+    ap.add_argument("--graphs", action="store_true",
+                    help="replay each ring from a CUDA graph instead of issuing every step from Python (N > 1)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -195,7 +195,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    use_graphs = world > 1 and not args.no_graphs
+    use_graphs = world > 1 and args.graphs
     enable_cuda_graphs(use_graphs)  # public switch of the operator: whole rings are captured once and replayed
     S1, SN, Hq, Hkv, Dqk, Dv, desc = WORKLOADS[args.workload]
     S = S1 if world == 1 else SN

@@ -1,8 +1,10 @@
 // HBM-bound kernels of the ring-attention path: the online-softmax merge of two partial
 // results, delta = rowsum(O * dO), and the final fp32 -> bf16 rounding of an accumulator.
-// Each thread moves 8 consecutive elements of one [b][s][h] row with 16-byte accesses;
-// consecutive threads walk the row, consecutive rows walk s, so both the row data and the
-// [B][H][S] statistics are read and written in whole sectors.
+// Each thread moves 8 consecutive elements of one [b][s][h] row with 16-byte accesses.
+// The grid is (blocks per plane, H, B): a block stays inside one (batch, head) plane and walks
+// consecutive s, so the row data and the [B][H][S] statistics are read and written in whole
+// sectors and all index arithmetic is 32-bit (a 64-bit divide per element would make these
+// kernels instruction-bound).
 #include "../../include/pith_b200.h"
 #include "common.cuh"
 #include "host_common.h"
@@ -33,21 +35,6 @@ __device__ __forceinline__ Vec8 load8(const void* base, int64_t elem_off) {
   return r;
 }
 
-struct RowIndex {
-  int b, s, h, chunk;
-};
-
-__device__ __forceinline__ RowIndex decode_item(int64_t item, int chunks, int S, int H) {
-  RowIndex r;
-  r.chunk = static_cast<int>(item % chunks);
-  int64_t row = item / chunks;
-  r.s = static_cast<int>(row % S);
-  row /= S;
-  r.h = static_cast<int>(row % H);
-  r.b = static_cast<int>(row / H);
-  return r;
-}
-
 struct CombineParams {
   const void* out1;
   const void* out2;
@@ -62,13 +49,21 @@ struct CombineParams {
 
 template <bool F32A, bool F32B, bool NATURAL>
 __global__ void __launch_bounds__(256) combine_kernel(const CombineParams p) {
-  const int chunks = p.D >> 3;
-  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.S * chunks;
-  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < total;
-       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const RowIndex r = decode_item(item, chunks, p.S, p.H);
-    const float l1 = __ldg(p.lse1 + r.b * p.l1s[0] + r.h * p.l1s[1] + r.s);
-    const float l2 = __ldg(p.lse2 + r.b * p.l2s[0] + r.h * p.l2s[1] + r.s);
+  const uint32_t chunks = static_cast<uint32_t>(p.D) >> 3;
+  const uint32_t plane = static_cast<uint32_t>(p.S) * chunks;  // items of one (b, h) plane
+  const int h = blockIdx.y, b = blockIdx.z;
+  const char* o1 = static_cast<const char*>(p.out1) + (b * p.o1s[0] + h * p.o1s[2]) * (F32A ? 4 : 2);
+  const char* o2 = static_cast<const char*>(p.out2) + (b * p.o2s[0] + h * p.o2s[2]) * (F32B ? 4 : 2);
+  const float* l1p = p.lse1 + b * p.l1s[0] + h * p.l1s[1];
+  const float* l2p = p.lse2 + b * p.l2s[0] + h * p.l2s[1];
+  float* outp = p.out + (static_cast<int64_t>(b) * p.S * p.H + h) * p.D;
+  float* lsep = p.lse + (static_cast<int64_t>(b) * p.H + h) * p.S;
+  const int64_t out_row = static_cast<int64_t>(p.H) * p.D;
+  for (uint32_t item = blockIdx.x * 256u + threadIdx.x; item < plane; item += gridDim.x * 256u) {
+    const uint32_t s = item / chunks, d0 = (item - s * chunks) << 3;
+    const float l1 = __ldg(l1p + s), l2 = __ldg(l2p + s);
+    const Vec8 a = load8<F32A>(o1, s * p.o1s[1] + d0);
+    const Vec8 c = load8<F32B>(o2, s * p.o2s[1] + d0);
     const float mx = fmaxf(l1, l2);
     float e1, e2, lse;
     if constexpr (NATURAL) {
@@ -81,16 +76,13 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams p) {
       lse = mx + log2f(e1 + e2);
     }
     const float den = e1 + e2;
-    const int d0 = r.chunk << 3;
-    const Vec8 a = load8<F32A>(p.out1, r.b * p.o1s[0] + r.s * p.o1s[1] + r.h * p.o1s[2] + d0);
-    const Vec8 c = load8<F32B>(p.out2, r.b * p.o2s[0] + r.s * p.o2s[1] + r.h * p.o2s[2] + d0);
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = (e1 * a.v[i] + e2 * c.v[i]) / den;
-    float4* dst = reinterpret_cast<float4*>(p.out + ((static_cast<int64_t>(r.b) * p.S + r.s) * p.H + r.h) * p.D + d0);
+    float4* dst = reinterpret_cast<float4*>(outp + s * out_row + d0);
     dst[0] = make_float4(o[0], o[1], o[2], o[3]);
     dst[1] = make_float4(o[4], o[5], o[6], o[7]);
-    if (r.chunk == 0) p.lse[(static_cast<int64_t>(r.b) * p.H + r.h) * p.S + r.s] = lse;
+    if (d0 == 0) lsep[s] = lse;
   }
 }
 
@@ -103,27 +95,29 @@ struct DeltaParams {
   int64_t ds[2];
 };
 
-// One 16-lane group per row when D = 128; the partial dot products are folded with shuffles.
+// `chunks` lanes (a power of two, 16 for D = 128) share one row; partial dot products are folded with shuffles.
 __global__ void __launch_bounds__(256) delta_kernel(const DeltaParams p) {
-  const int chunks = p.D >> 3;  // power of two <= 32 (checked on the host)
-  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.S * chunks;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  const int64_t rounds = (total + stride - 1) / stride;
-  int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-  for (int64_t it = 0; it < rounds; ++it, item += stride) {
+  const uint32_t chunks = static_cast<uint32_t>(p.D) >> 3;  // power of two <= 32 (checked on the host)
+  const uint32_t plane = static_cast<uint32_t>(p.S) * chunks;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const __nv_bfloat16* op = static_cast<const __nv_bfloat16*>(p.o) + b * p.os[0] + h * p.os[2];
+  const __nv_bfloat16* dp = static_cast<const __nv_bfloat16*>(p.dout) + b * p.dos[0] + h * p.dos[2];
+  float* out = p.delta + b * p.ds[0] + h * p.ds[1];
+  const uint32_t stride = gridDim.x * 256u;
+  const uint32_t rounds = (plane + stride - 1) / stride;
+  uint32_t item = blockIdx.x * 256u + threadIdx.x;
+  for (uint32_t it = 0; it < rounds; ++it, item += stride) {
     float acc = 0.f;
-    RowIndex r = {0, 0, 0, 0};
-    const bool live = item < total;
+    const bool live = item < plane;
+    const uint32_t s = item / chunks, d0 = (item - s * chunks) << 3;
     if (live) {
-      r = decode_item(item, chunks, p.S, p.H);
-      const int d0 = r.chunk << 3;
-      const Vec8 a = load8<false>(p.o, r.b * p.os[0] + r.s * p.os[1] + r.h * p.os[2] + d0);
-      const Vec8 c = load8<false>(p.dout, r.b * p.dos[0] + r.s * p.dos[1] + r.h * p.dos[2] + d0);
+      const Vec8 a = load8<false>(op, s * p.os[1] + d0);
+      const Vec8 c = load8<false>(dp, s * p.dos[1] + d0);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc = fmaf(a.v[i], c.v[i], acc);
     }
-    for (int off = chunks >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
-    if (live && r.chunk == 0) p.delta[r.b * p.ds[0] + r.h * p.ds[1] + r.s] = acc;
+    for (uint32_t off = chunks >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, off);
+    if (live && d0 == 0) out[s] = acc;
   }
 }
 
@@ -135,34 +129,36 @@ struct CastParams {
   float scale;
 };
 
+// Grid (blocks per batch, 1, B); rows are walked in storage order (s, h).
 __global__ void __launch_bounds__(256) cast_kernel(const CastParams p) {
-  const int chunks = p.D >> 3;
-  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.S * chunks;
-  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < total;
-       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    // rows ordered (b, s, h) here: both tensors are walked in their storage order
-    const int chunk = static_cast<int>(item % chunks);
-    int64_t row = item / chunks;
-    const int h = static_cast<int>(row % p.H);
-    row /= p.H;
-    const int s = static_cast<int>(row % p.S);
-    const int b = static_cast<int>(row / p.S);
-    const int d0 = chunk << 3;
-    const Vec8 a = load8<true>(p.acc, b * p.as[0] + s * p.as[1] + h * p.as[2] + d0);
+  const uint32_t chunks = static_cast<uint32_t>(p.D) >> 3;
+  const uint32_t H = static_cast<uint32_t>(p.H);
+  const uint32_t plane = static_cast<uint32_t>(p.S) * H * chunks;
+  const int b = blockIdx.z;
+  const float* src = p.acc + b * p.as[0];
+  __nv_bfloat16* dst = p.out + b * p.os[0];
+  for (uint32_t item = blockIdx.x * 256u + threadIdx.x; item < plane; item += gridDim.x * 256u) {
+    const uint32_t row = item / chunks, d0 = (item - row * chunks) << 3;
+    const uint32_t s = row / H, h = row - s * H;
+    const Vec8 a = load8<true>(src, s * p.as[1] + h * p.as[2] + d0);
     uint4 u;
     u.x = pack_bf16(a.v[0] * p.scale, a.v[1] * p.scale);
     u.y = pack_bf16(a.v[2] * p.scale, a.v[3] * p.scale);
     u.z = pack_bf16(a.v[4] * p.scale, a.v[5] * p.scale);
     u.w = pack_bf16(a.v[6] * p.scale, a.v[7] * p.scale);
-    *reinterpret_cast<uint4*>(p.out + b * p.os[0] + s * p.os[1] + h * p.os[2] + d0) = u;
+    *reinterpret_cast<uint4*>(dst + s * p.os[1] + h * p.os[2] + d0) = u;
   }
 }
 
-static int grid_for(int64_t total_items) {
-  // 148 SMs x 8 resident 256-thread blocks; fewer when the problem is smaller.
-  int64_t blocks = (total_items + 255) / 256;
-  const int64_t cap = 148 * 8;
-  return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+// Blocks along x for `planes` planes of `plane_items` items: about 148 SMs x 8 resident blocks in total.
+static dim3 grid_for(int64_t plane_items, int planes_y, int planes_z) {
+  int64_t need = (plane_items + 255) / 256;
+  int64_t planes = static_cast<int64_t>(planes_y) * planes_z;
+  int64_t cap = (148 * 8 + planes - 1) / planes;
+  if (cap < 1) cap = 1;
+  int64_t bx = need < cap ? need : cap;
+  if (bx < 1) bx = 1;
+  return dim3(static_cast<unsigned>(bx), static_cast<unsigned>(planes_y), static_cast<unsigned>(planes_z));
 }
 
 static bool rows_ok(const void* base, const int64_t st[3], int elem_bytes) {
@@ -192,7 +188,8 @@ extern "C" int pith_combine(const pith_combine_args* a, void* stream) {
   for (int i = 0; i < 3; ++i) { p.o1s[i] = a->out1_stride[i]; p.o2s[i] = a->out2_stride[i]; }
   for (int i = 0; i < 2; ++i) { p.l1s[i] = a->lse1_stride[i]; p.l2s[i] = a->lse2_stride[i]; }
   const int64_t items = static_cast<int64_t>(a->B) * a->S * a->H * (a->D / 8);
-  const int grid = grid_for(items);
+  PITH_REQUIRE(a->H <= 65535 && a->B <= 65535 && items / a->H / a->B < (1ll << 32), "tensor too large for one launch");
+  const dim3 grid = grid_for(static_cast<int64_t>(a->S) * (a->D / 8), a->H, a->B);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool nat = (a->flags & PITH_COMBINE_NATURAL) != 0;
   const int sel = (a->out1_dtype == PITH_DTYPE_F32 ? 4 : 0) | (a->out2_dtype == PITH_DTYPE_F32 ? 2 : 0) | (nat ? 1 : 0);
@@ -227,7 +224,8 @@ extern "C" int pith_attn_bwd_preprocess(const pith_bwd_preprocess_args* a, void*
   for (int i = 0; i < 3; ++i) { p.os[i] = a->o_stride[i]; p.dos[i] = a->do_stride[i]; }
   p.ds[0] = a->delta_stride[0]; p.ds[1] = a->delta_stride[1];
   const int64_t items = static_cast<int64_t>(a->B) * a->S * a->H * chunks;
-  delta_kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PITH_REQUIRE(a->H <= 65535 && a->B <= 65535 && items / a->H / a->B < (1ll << 32), "tensor too large for one launch");
+  delta_kernel<<<grid_for(static_cast<int64_t>(a->S) * chunks, a->H, a->B), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PITH_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -246,7 +244,8 @@ extern "C" int pith_cast_f32_to_bf16(const float* acc, void* out, int32_t B, int
   p.B = B; p.S = S; p.H = H; p.D = D; p.scale = scale;
   for (int i = 0; i < 3; ++i) { p.as[i] = acc_stride[i]; p.os[i] = out_stride[i]; }
   const int64_t items = static_cast<int64_t>(B) * S * H * (D / 8);
-  cast_kernel<<<grid_for(items), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  PITH_REQUIRE(B <= 65535 && items / B < (1ll << 32), "tensor too large for one launch");
+  cast_kernel<<<grid_for(static_cast<int64_t>(S) * H * (D / 8), 1, B), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   PITH_CUDA(cudaGetLastError());
   return kOk;
 }
