@@ -287,10 +287,30 @@ def main():
     roofline = {
         "bound": "tensor", "kernel": dom, "achieved": kern[dom]["tflops"], "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
         "frac": kern[dom]["tflops"] / pk["bf16_tflops"], "peak_source": pk["source"] + " burst (kernel timed alone)",
-        "traffic": None, "kernels": kern,
+        # DRAM read + write bytes of one dK/dV launch at this exact workload, from the ncu capture summarised in
+        # profiles/attention_kernels_qwen3_s8192.md (only known for the N = 1 Qwen3 case)
+        "traffic": 208.1e6 if (world == 1 and args.workload == "qwen3" and "kDkDv" in dom) else None,
+        "traffic_unit": "DRAM bytes per launch (ncu)", "kernels": kern,
         "note": "algorithmic FLOPs per launch: causal block B*H*S^2*(Dqk+Dv) x {fwd 1, dK/dV 2, dQ 0.5}; "
                 "the dQ launch recomputes S and dP (not counted)",
     }
+
+    # ---- HBM-bound kernels of the path, timed alone: algorithmic bytes / time against the measured copy bandwidth
+    n_row = S_loc * Hq
+    acc_f32 = torch.randn(1, S_loc, Hq, Dv, device=dev)
+    hbm_runs = {
+        "combine_kernel (fp32 + bf16 -> fp32, log2)": (
+            lambda: kernels.combine(acc_f32, lse_d, out_d, lse_d, natural=False), n_row * Dv * (4 + 2 + 4) + 12 * n_row),
+        "delta_kernel": (lambda: kernels.bwd_preprocess(out_d, do, delta_d), n_row * Dv * 4 + 4 * n_row),
+        "cast_kernel (dQ)": (lambda: kernels.cast_to_bf16(dq_acc), n_row * Dqk * 6),
+    }
+    hbm = {}
+    for name, (run, nbytes) in hbm_runs.items():
+        for _ in range(3):
+            run()
+        kms = timed(run, 10)
+        hbm[name] = {"us": kms * 1e3, "gbs": nbytes / (kms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (kms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    roofline["hbm_kernels"] = hbm
 
     # ---- comm / compute overlap of one ring (N > 1): compute alone, exchanges alone, both
     overlap = None
