@@ -189,6 +189,41 @@ int pith_attn_bwd_noalloc(const pith_attn_bwd_noalloc_args* args, void* stream);
 size_t pith_attn_bwd_noalloc_scratch_bytes(int32_t B, int32_t Sq, int32_t Sk, int32_t Hq, int32_t Hkv, int32_t Dqk,
                                            int32_t Dv);
 
+/*
+ * Stream-ordered hand-off flags for moving ring blocks with the copy engines instead of NCCL kernels.
+ * Replace: the `req.wait()` on the NCCL requests in `_ring_send_recv_kv`
+ *   (pithtrain/operators/ring_attention/standard.py:46-50) and in the dK/dV redistribution (:183-184).
+ * Every flag has a sequence counter on each side, in that side's own memory; both start at 0 and advance by one per
+ * call, on the device, so the same launches can be replayed from a CUDA graph.
+ * pith_flag_signal: in stream order, ++*counter (local memory), publishes all earlier work of `stream` system-wide,
+ *   then stores the new *counter into `flag` (which may be mapped memory of a peer GPU).
+ * pith_flag_wait: in stream order, ++*counter (local memory), then `stream` waits until the LOCAL `flag` reaches
+ *   *counter (wrap-safe). The wait gives up after about `max_seconds` (at most 120), records code 3 in *status and
+ *   lets the stream continue.
+ * pith_enable_peer_access: enables direct access from the current device to `peer_device` (idempotent).
+ */
+int pith_flag_signal(uint32_t* flag, uint32_t* counter, void* stream);
+int pith_flag_wait(const uint32_t* flag, uint32_t* counter, double max_seconds, uint32_t* status, void* stream);
+int pith_enable_peer_access(int32_t peer_device);
+
+/*
+ * Sharing ring buffers between the processes of one node (CUDA IPC) and copying between them.
+ * Replace: `dist.batch_isend_irecv` in `_ring_send_recv_kv` (pithtrain/operators/ring_attention/standard.py:37-45),
+ *   which moves the same bytes through NCCL send/recv kernels.
+ * pith_ipc_export: writes the 64-byte IPC handle of the device allocation that contains `ptr` into `handle64`
+ *   and the byte offset of `ptr` inside that allocation into *offset.
+ * pith_ipc_open: maps the allocation behind a handle exported by ANOTHER process into the current device's
+ *   address space; *base receives the mapped start of the allocation. One open per handle per process.
+ * pith_ipc_close: unmaps what pith_ipc_open returned.
+ * pith_peer_copy: enqueues a device-to-device copy of `bytes` on `stream` (copy engine; `src` or `dst` may be
+ *   peer-mapped memory).
+ */
+#define PITH_IPC_HANDLE_BYTES 64
+int pith_ipc_export(const void* ptr, void* handle64, uint64_t* offset);
+int pith_ipc_open(const void* handle64, void** base);
+int pith_ipc_close(void* base);
+int pith_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
+
 /* Text of the last host-side rejection on the calling thread. */
 const char* pith_last_error(void);
 /* Human-readable form of a device status word. Returns a pointer to a thread-local buffer. */

@@ -80,6 +80,8 @@ const char* pith_status_string(uint32_t status) {
     snprintf(buf, sizeof buf, "ok");
   else if (code == pith::kErrWaitTimeout)
     snprintf(buf, sizeof buf, "device wait timed out (barrier tag 0x%06x)", detail);
+  else if (code == 3u)
+    snprintf(buf, sizeof buf, "wait for a ring neighbour timed out (sequence number 0x%06x)", detail);
   else if (code == pith::kErrTmemAlloc)
     snprintf(buf, sizeof buf, "unexpected TMEM allocation (0x%06x)", detail);
   else

@@ -93,6 +93,13 @@ EXPORTS = {
     "pith_combine": (c_int, [POINTER(CombineArgs), c_void_p]),
     "pith_attn_bwd_noalloc": (c_int, [POINTER(AttnBwdNoallocArgs), c_void_p]),
     "pith_attn_bwd_noalloc_scratch_bytes": (ctypes.c_size_t, [c_int32] * 7),
+    "pith_flag_signal": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "pith_flag_wait": (c_int, [c_void_p, c_void_p, ctypes.c_double, c_void_p, c_void_p]),
+    "pith_enable_peer_access": (c_int, [c_int32]),
+    "pith_ipc_export": (c_int, [c_void_p, c_void_p, POINTER(ctypes.c_uint64)]),
+    "pith_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "pith_ipc_close": (c_int, [c_void_p]),
+    "pith_peer_copy": (c_int, [c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
     "pith_last_error": (c_char_p, []),
     "pith_status_string": (c_char_p, [c_uint32]),
     "pith_abi_version": (c_int, []),

@@ -73,10 +73,23 @@ class RingComm:
             r.wait()
 
 
-def _pack_kv(k, v):
+def _begin(comm, nbytes: int) -> None:
+    """Tells a communicator that owns its ring buffers how much one ring needs."""
+    if hasattr(comm, "begin"):
+        comm.begin(nbytes)
+
+
+def _ring_buffer(comm, numel: int, dtype, device):
+    """A buffer that takes part in exchanges: from the communicator's arena if it has one."""
+    if hasattr(comm, "empty"):
+        return comm.empty(numel, dtype)
+    return torch.empty(numel, dtype=dtype, device=device)
+
+
+def _pack_kv(comm, k, v):
     """Two ping-pong buffers holding [K | V] back to back; the first is filled from (k, v)."""
     nk, nv = k.numel(), v.numel()
-    bufs = [torch.empty(nk + nv, dtype=k.dtype, device=k.device) for _ in range(2)]
+    bufs = [_ring_buffer(comm, nk + nv, k.dtype, k.device) for _ in range(2)]
     bufs[0][:nk].view(k.shape).copy_(k)
     bufs[0][nk:].view(v.shape).copy_(v)
     return bufs, nk
@@ -99,7 +112,8 @@ def ring_forward(backend, comm: RingComm, q, k, v, scale: float, cp_rank: int, c
     if sharding == "zigzag" and S % 2:
         raise ValueError(f"zigzag sharding needs an even local sequence length, got {S}")
     c = S // 2
-    bufs, nk = _pack_kv(k, v)
+    _begin(comm, 2 * (k.numel() + v.numel()) * k.element_size())
+    bufs, nk = _pack_kv(comm, k, v)
     acc = torch.empty((B, S, Hq, Dv), dtype=torch.float32, device=q.device)
     cur = 0
     for t in range(cp_size):
@@ -135,8 +149,9 @@ def ring_backward(backend, comm: RingComm, q, k, v, out, lse, dout, scale: float
         backend.bwd_block(q, k, v, dout, lse, delta, scale, True, dq_acc, dk_acc, dv_acc)
         return backend.cast(dq_acc).to(q.dtype), backend.cast(dk_acc).to(k.dtype), backend.cast(dv_acc).to(v.dtype)
     c = S // 2
-    bufs, _ = _pack_kv(k, v)
-    grads = [torch.empty(nk + nv, dtype=torch.float32, device=q.device) for _ in range(3)]
+    _begin(comm, (nk + nv) * (2 * k.element_size() + 3 * 4))
+    bufs, _ = _pack_kv(comm, k, v)
+    grads = [_ring_buffer(comm, nk + nv, torch.float32, q.device) for _ in range(3)]
     cur = 0
     for t in range(cp_size):
         src = (cp_rank - t) % cp_size
@@ -233,6 +248,45 @@ class _GraphedCall:
         return tuple(o.clone() for o in self.static_out)
 
 
+# ----------------------------------------------------------------------------- copy-engine exchanges (opt-in)
+_peer_enabled = _os.environ.get("PITH_B200_RING_PEER_COPIES", "0") == "1"
+_peer_group = None
+_peer_comms: dict = {}
+
+
+def enable_peer_copies(flag: bool = True, group=None) -> None:
+    """Move ring blocks with the copy engines over peer-mapped memory instead of NCCL send/recv (single node).
+
+    ``group`` is the process group used once per ring to exchange memory handles (default: the world group); it
+    must contain the ring's ranks, and all its ranks must run the first ring attention call together."""
+    global _peer_enabled, _peer_group
+    _peer_enabled = bool(flag)
+    _peer_group = group
+
+
+def peer_copies_enabled() -> bool:
+    return _peer_enabled
+
+
+def release_peer_copies() -> None:
+    """Unmaps the neighbours' buffers (collective). Call before destroying the process group."""
+    release_cuda_graphs()
+    for comm in _peer_comms.values():
+        comm.close()
+    _peer_comms.clear()
+
+
+def _make_comm(cp_rank, cp_size, global_ranks, device):
+    if not (_peer_enabled and cp_size > 1 and device.type == "cuda"):
+        return RingComm(cp_rank, cp_size, global_ranks, device)
+    key = (cp_rank, cp_size, tuple(global_ranks), device.index)
+    comm = _peer_comms.get(key)
+    if comm is None:
+        from ._peer import PeerRingComm
+        comm = _peer_comms[key] = PeerRingComm(cp_rank, cp_size, global_ranks, device, group=_peer_group)
+    return comm
+
+
 def _use_graph(q) -> bool:
     return _graphs_enabled and q.is_cuda and not torch.cuda.is_current_stream_capturing()
 
@@ -245,7 +299,7 @@ def _key(kind, tensors, scale, cp_rank, cp_size, global_ranks, sharding):
 def ring_forward_auto(q, k, v, scale, cp_rank, cp_size, global_ranks, sharding):
     """ring_forward on the CUDA backend, replayed from a graph when graphs are enabled and CP > 1."""
     backend = CudaBlockBackend()
-    comm = RingComm(cp_rank, cp_size, global_ranks, q.device)
+    comm = _make_comm(cp_rank, cp_size, global_ranks, q.device)
     if cp_size == 1 or not _use_graph(q):
         return ring_forward(backend, comm, q, k, v, scale, cp_rank, cp_size, sharding)
     key = _key("fwd", (q, k, v), scale, cp_rank, cp_size, global_ranks, sharding)
@@ -260,7 +314,7 @@ def ring_forward_auto(q, k, v, scale, cp_rank, cp_size, global_ranks, sharding):
 def ring_backward_auto(q, k, v, out, lse, dout, scale, cp_rank, cp_size, global_ranks, sharding):
     """ring_backward on the CUDA backend, replayed from a graph when graphs are enabled and CP > 1."""
     backend = CudaBlockBackend()
-    comm = RingComm(cp_rank, cp_size, global_ranks, q.device)
+    comm = _make_comm(cp_rank, cp_size, global_ranks, q.device)
     if cp_size == 1 or not _use_graph(q):
         return ring_backward(backend, comm, q, k, v, out, lse, dout, scale, cp_rank, cp_size, sharding)
     key = _key("bwd", (q, k, v, out, lse, dout), scale, cp_rank, cp_size, global_ranks, sharding)

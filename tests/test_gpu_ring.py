@@ -3,6 +3,7 @@ the box has at least two GPUs, real NCCL ranks through the public operator API."
 
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -144,3 +145,86 @@ def test_ring_over_nccl(cuda_device, tmp_path):
             assert_bf16_close(got, full[name], f"{tag} {name}")
             # the reference's own ring test metric (tests/test_ring_attention.py:91): cosine error < 1e-5
             assert O.cosine_error(got, full[name]) < 1e-5, (tag, name)
+
+
+def test_flag_wait_is_bounded_and_reports(cuda_device):
+    """A wait on a flag that nothing sets gives up after its limit and records code 3; the context stays usable.
+    A signal followed by a wait on the same stream (stream order, so nothing spins) passes silently."""
+    from pithtrain_b200 import _lib, kernels
+    lib = _lib.load()
+    flag = torch.zeros(2, dtype=torch.int32, device=cuda_device)
+    ctr = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):  # signal n, then wait for n: already satisfied
+        _lib.check(lib.pith_flag_signal(flag.data_ptr(), ctr.data_ptr(), s), "signal")
+        _lib.check(lib.pith_flag_wait(flag.data_ptr(), ctr.data_ptr() + 4, 0.2, status.data_ptr(), s), "wait")
+    torch.cuda.synchronize()
+    assert flag[0].item() == 3 and ctr[:2].tolist() == [3, 3] and status.item() == 0
+    t0 = time.perf_counter()
+    _lib.check(lib.pith_flag_wait(flag.data_ptr() + 4, ctr.data_ptr() + 8, 0.2, status.data_ptr(), s), "wait")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    word = status.item() & 0xFFFFFFFF
+    assert word >> 24 == 3 and (word & 0xFFFFFF) == 1
+    assert b"neighbour" in lib.pith_status_string(word)
+    assert lib.pith_flag_wait(0, ctr.data_ptr(), 0.2, 0, s) != 0  # null flag rejected on the host
+    assert lib.pith_flag_wait(flag.data_ptr(), ctr.data_ptr(), 1e9, 0, s) != 0  # unbounded wait rejected
+    assert torch.ones(4, device=cuda_device).sum().item() == 4.0
+
+
+def _peer_worker(rank, world, port, path):
+    import torch.distributed as dist
+    from pithtrain_b200 import kernels
+    from pithtrain_b200.operators import ring_attention as ra
+    from pithtrain_b200.operators.ring_attention import sharding as sh
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        group = dist.new_group(list(range(world)))
+        ra.enable_peer_copies(True, group)
+        results = {}
+        for tag, fn, (hq, hkv, dqk), layout in (("gqa_zigzag", ra.ring_attention_func, (8, 2, 128), "zigzag"),
+                                                 ("mla_contiguous", ra.ring_mla_attention_func, (16, 16, 192),
+                                                  "contiguous")):
+            q, k, v, do = _problem(512 * world, hq, hkv, dqk)
+            loc = lambda t: sh.shard_sequence(t, world, rank, layout).contiguous().to(dev)  # noqa: E731
+            ql, kl, vl, dol = loc(q).requires_grad_(), loc(k).requires_grad_(), loc(v).requires_grad_(), loc(do)
+            for graphs in (False, True):
+                ra.enable_cuda_graphs(graphs)
+                for _ in range(3 if graphs else 2):  # with graphs: capture at the first call, then two replays
+                    ql.grad = kl.grad = vl.grad = None
+                    out = fn(ql, kl, vl, dqk ** -0.5, group, layout)
+                    out.backward(dol)
+                torch.cuda.synchronize()
+                kernels.check_device_status(dev)
+                results[tag + ("_graph" if graphs else "")] = [t.detach().cpu()
+                                                               for t in (out, ql.grad, kl.grad, vl.grad)]
+            ra.enable_cuda_graphs(False)
+        torch.save(results, os.path.join(path, f"rank{rank}.pt"))
+        ra.release_peer_copies()
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ring_over_peer_copies(cuda_device, tmp_path):
+    """Ring blocks moved by the copy engines over IPC-mapped peer memory, eager and replayed from CUDA graphs."""
+    import torch.multiprocessing as mp
+    from pithtrain_b200.operators.ring_attention import sharding as sh
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_peer_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    res = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    for base, (hq, hkv, dqk), layout in (("gqa_zigzag", (8, 2, 128), "zigzag"),
+                                         ("mla_contiguous", (16, 16, 192), "contiguous")):
+        q, k, v, do = _problem(512 * world, hq, hkv, dqk)
+        full = O.full_attention_fwd_bwd(q, k, v, do, dqk ** -0.5)
+        for tag in (base, base + "_graph"):
+            for i, name in enumerate(("o", "dq", "dk", "dv")):
+                got = sh.unshard_sequence([r[tag][i] for r in res], layout, seq_dim=1)
+                assert_bf16_close(got, full[name], f"{tag} {name}")
+                assert O.cosine_error(got, full[name]) < 1e-5, (tag, name)
