@@ -53,35 +53,50 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs: a thread every
+    20 ms plus one explicit sample taken while the timed work is still in flight."""
 
     def __init__(self, index: int):
         self.rows = []
-        self.proc = None
         self.index = index
+        self.nv = self.handle = None
+        self.stop = threading.Event()
+        self.thread = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
-                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv, self.handle = pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.thread = threading.Thread(target=self._loop, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:  # no NVML: the summary says so (samples = 0)
+            self.nv = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+    def sample(self):
+        nv = self.nv
+        if nv is None:
+            return
+        try:
+            sm = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+            mx = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
+            bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:
+            return
+        flag = lambda name: "Active" if bits & getattr(nv, name, 0) else "Not Active"  # noqa: E731
+        self.rows.append([str(sm), str(mx), flag("nvmlClocksEventReasonHwSlowdown"),
+                          flag("nvmlClocksEventReasonHwThermalSlowdown"),
+                          flag("nvmlClocksEventReasonSwThermalSlowdown"), flag("nvmlClocksEventReasonSwPowerCap")])
+
+    def _loop(self):
+        while not self.stop.is_set():
+            self.sample()
+            self.stop.wait(0.02)
 
     def __exit__(self, *exc):
-        if self.proc is not None:
-            time.sleep(0.15)
-            self.proc.terminate()
+        self.stop.set()
+        if self.thread is not None:
             self.thread.join(timeout=2)
 
     def summary(self):
@@ -170,6 +185,9 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="skip the comm/compute overlap measurement (N > 1)")
     ap.add_argument("--graphs", action="store_true",
                     help="replay each ring from a CUDA graph instead of issuing every step from Python (N > 1)")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="how ring blocks travel at N > 1: copy engines over peer-mapped memory (one node), or NCCL "
+                         "send/recv")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -186,7 +204,8 @@ def main():
     import torch.distributed as dist
     from pithtrain_b200 import build, kernels
     from pithtrain_b200.operators.ring_attention import (RingAttentionFunc, RingMLAAttentionFunc, _ring,
-                                                         enable_cuda_graphs, release_cuda_graphs)
+                                                         enable_cuda_graphs, enable_peer_copies,
+                                                         release_cuda_graphs, release_peer_copies)
 
     build.build_library()
     dev = torch.device("cuda", local_rank)
@@ -197,6 +216,8 @@ def main():
 
     use_graphs = world > 1 and args.graphs
     enable_cuda_graphs(use_graphs)  # public switch of the operator: whole rings are captured once and replayed
+    use_peer = world > 1 and args.exchange == "peer"
+    enable_peer_copies(use_peer)    # public switch: exchanges run on the copy engines, not in NCCL kernels
     S1, SN, Hq, Hkv, Dqk, Dv, desc = WORKLOADS[args.workload]
     S = S1 if world == 1 else SN
     S_loc = S // world
@@ -220,7 +241,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(run, steps):
+    def timed(run, steps, in_flight=None):
         """Device time of `steps` calls of run(), max over ranks, in ms per call."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -228,6 +249,8 @@ def main():
         for _ in range(steps):
             run()
         e1.record()
+        if in_flight is not None:
+            in_flight()  # called while the last steps still run on the GPU
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
         if world > 1:
@@ -240,7 +263,7 @@ def main():
     kernels.check_device_status(dev)
     launches0 = kernels.launch_count
     with ClockSampler(local_rank) as clk:
-        ms = timed(lambda: step(q, k, v, do), args.steps)
+        ms = timed(lambda: step(q, k, v, do), args.steps, clk.sample)
     launches = (kernels.launch_count - launches0) // args.steps
     kernels.check_device_status(dev)
     flops_total = fwd_bwd_flops(S, Hq, Dqk, Dv)
@@ -337,7 +360,7 @@ def main():
                 return torch.empty(acc.shape, dtype=torch.bfloat16, device=acc.device)
 
         be, nocompute = _ring.CudaBlockBackend(), NoCompute()
-        comm, nocomm = _ring.RingComm(rank, world, global_ranks, dev), NoComm()
+        comm, nocomm = _ring._make_comm(rank, world, global_ranks, dev), NoComm()
 
         def ring(b, c):
             o, l = _ring.ring_forward(b, c, qd, kd, vd, scale, rank, world, args.sharding)
@@ -378,6 +401,7 @@ def main():
                     else f"{args.sharding} CP={world}" if world > 1 else "single GPU (CP=1)"),
                 "sharding": args.sharding if world > 1 else "none",
                 "ring_cuda_graphs": use_graphs,
+                "ring_exchange": "copy engines over peer-mapped memory" if use_peer else "NCCL send/recv",
                 "l2": "inputs + gradients per step exceed the 126 MB L2 (no flush needed)",
                 "flops_convention": "fwd B*H*S^2*(Dqk+Dv), bwd 2.5x fwd",
             },
@@ -398,6 +422,7 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         release_cuda_graphs()
+        release_peer_copies()
         dist.barrier()
         dist.destroy_process_group()
 

@@ -283,7 +283,9 @@ def _make_comm(cp_rank, cp_size, global_ranks, device):
     comm = _peer_comms.get(key)
     if comm is None:
         from ._peer import PeerRingComm
-        comm = _peer_comms[key] = PeerRingComm(cp_rank, cp_size, global_ranks, device, group=_peer_group)
+        wait_seconds = float(_os.environ.get("PITH_B200_RING_WAIT_SECONDS", "30"))
+        comm = _peer_comms[key] = PeerRingComm(cp_rank, cp_size, global_ranks, device, group=_peer_group,
+                                               wait_seconds=wait_seconds)
     return comm
 
 
