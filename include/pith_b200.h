@@ -18,7 +18,8 @@
  *  - Return value: 0 = enqueued; negative = rejected on the host (pith_last_error() has the
  *    text). Device-side anomalies (a bounded wait that ran out) are written to *status
  *    (a zero-initialised device uint32, optional) as (code << 24 | detail); see pith_status_string.
- *  - Re-entrant; no internal threads; no global mutable state besides a cache of TMA descriptors.
+ *  - Re-entrant; no internal threads; no global mutable state besides a cache of TMA descriptors and, per device,
+ *    one side stream with two events used by pith_attn_bwd (created on first use).
  */
 #ifndef PITH_B200_H_
 #define PITH_B200_H_
@@ -35,6 +36,13 @@ extern "C" {
 /* flags for pith_attn_fwd_args.flags */
 #define PITH_FWD_O_FP32 1u        /* `o` is fp32 (running accumulator of a ring) instead of bf16 */
 #define PITH_FWD_LSE_NATURAL 2u   /* write natural-log LSE (flash-attn convention) instead of log2 */
+
+/* flags for pith_attn_bwd_args.flags */
+#define PITH_BWD_SERIAL 1u        /* run the dK/dV and dQ passes one after the other on `stream` */
+#define PITH_BWD_CONCURRENT 2u    /* run the dQ pass beside the dK/dV pass on a side stream the library keeps per
+                                     device, joined into `stream` before the call returns.
+                                     Neither flag: the library decides by problem size (side by side for launches of
+                                     a few waves, where the partial last wave matters). */
 
 /* flags for pith_combine_args.flags */
 #define PITH_COMBINE_NATURAL 1u   /* LSEs are natural-log (standard.py) instead of log2 (mla.py) */

@@ -103,6 +103,7 @@ extern "C" int pith_attn_bwd_noalloc(const pith_attn_bwd_noalloc_args* a, void* 
   b.dq_acc = dq_acc; b.dk_acc = dk_acc; b.dv_acc = dv_acc; b.status = a->status;
   b.B = a->B; b.Sq = a->Sq; b.Sk = a->Sk; b.Hq = a->Hq; b.Hkv = a->Hkv; b.Dqk = a->Dqk; b.Dv = a->Dv;
   b.causal = a->causal; b.causal_offset = a->causal_offset; b.softmax_scale = a->softmax_scale;
+  b.flags = PITH_BWD_SERIAL;  // one stream, no side stream or events
   const int64_t dq_st[3] = {static_cast<int64_t>(a->Sq) * a->Hq * a->Dqk, static_cast<int64_t>(a->Hq) * a->Dqk, a->Dqk};
   const int64_t dk_st[3] = {static_cast<int64_t>(a->Sk) * a->Hkv * a->Dqk, static_cast<int64_t>(a->Hkv) * a->Dqk, a->Dqk};
   const int64_t dv_st[3] = {static_cast<int64_t>(a->Sk) * a->Hkv * a->Dv, static_cast<int64_t>(a->Hkv) * a->Dv, a->Dv};

@@ -120,8 +120,11 @@ def bwd_preprocess(o, dout, delta=None):
 
 
 def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool, causal_offset: int,
-             dq_acc, dk_acc, dv_acc, debug=None):
-    """Adds this block's dQ/dK/dV into the fp32 accumulators; see ``pith_attn_bwd``."""
+             dq_acc, dk_acc, dv_acc, debug=None, serial=None):
+    """Adds this block's dQ/dK/dV into the fp32 accumulators; see ``pith_attn_bwd``.
+
+    ``serial=True`` runs the two passes one after the other on the current stream (``PITH_BWD_SERIAL``),
+    ``serial=False`` side by side (``PITH_BWD_CONCURRENT``); ``None`` lets the library decide by problem size."""
     _require_cuda(q, k, v, dout, lse_log2, delta, dq_acc, dk_acc, dv_acc)
     B, Sq, Hq, Dqk = q.shape
     _, Sk, Hkv, Dv = v.shape
@@ -137,7 +140,7 @@ def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool,
     a.status = status_word(q.device).data_ptr()
     a.debug = debug.data_ptr() if debug is not None else None
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
-    a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), 0
+    a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), (0 if serial is None else _lib.BWD_SERIAL if serial else _lib.BWD_CONCURRENT)
     a.softmax_scale = float(softmax_scale)
     a.q_stride, a.k_stride, a.v_stride, a.do_stride = _bshd(q, "q"), _bshd(k, "k"), _bshd(v, "v"), _bshd(dout, "dout")
     if dq_acc is not None:
