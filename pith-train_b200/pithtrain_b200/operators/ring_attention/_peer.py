@@ -19,6 +19,7 @@ buffer has the same arena offset on both sides). Single node only (CUDA IPC).
 from __future__ import annotations
 
 import ctypes
+import socket
 
 import torch
 import torch.distributed as dist
@@ -54,7 +55,12 @@ class PeerRingComm:
         self.counters = torch.zeros(4 * _NFLAGS, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         with torch.cuda.device(self.device):
-            shared = self._all_gather(self._export(self.flags))
+            shared = self._all_gather(self._export(self.flags) + (socket.gethostname(),))
+            hosts = {shared[self._index_in_group(r)][3] for r in range(self.size)}
+            if len(hosts) > 1:  # the same on every rank, so all of them raise
+                raise RuntimeError(f"peer-copy ring exchange needs all ranks of the ring on one node, got {sorted(hosts)}; "
+                                   "keep the NCCL exchange (enable_peer_copies(False))")
+            shared = [x[:3] for x in shared]
             self._prev_flags = self._map(shared[self._index_in_group(self.rank - 1)])
             self._next_flags = self._map(shared[self._index_in_group(self.rank + 1)])
         dist.barrier(group=self.group)

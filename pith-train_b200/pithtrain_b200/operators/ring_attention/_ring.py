@@ -252,16 +252,23 @@ class _GraphedCall:
 _peer_enabled = _os.environ.get("PITH_B200_RING_PEER_COPIES", "0") == "1"
 _peer_group = None
 _peer_comms: dict = {}
+_ring_groups: dict = {}
 
 
 def enable_peer_copies(flag: bool = True, group=None) -> None:
     """Move ring blocks with the copy engines over peer-mapped memory instead of NCCL send/recv (single node).
 
-    ``group`` is the process group used once per ring to exchange memory handles (default: the world group); it
-    must contain the ring's ranks, and all its ranks must run the first ring attention call together."""
+    ``group`` is the process group used once per ring to exchange memory handles. Default: the ``cp_group`` given
+    to ``ring_attention_func`` / ``ring_mla_attention_func``, or the world group when the autograd functions are
+    called directly. It must contain the ring's ranks, and all its ranks must make the first ring call together."""
     global _peer_enabled, _peer_group
     _peer_enabled = bool(flag)
     _peer_group = group
+
+
+def register_group(global_ranks, group) -> None:
+    """Remembers the process group of a ring so that the peer exchange can set itself up over exactly its ranks."""
+    _ring_groups[tuple(global_ranks)] = group
 
 
 def peer_copies_enabled() -> bool:
@@ -284,7 +291,7 @@ def _make_comm(cp_rank, cp_size, global_ranks, device):
     if comm is None:
         from ._peer import PeerRingComm
         wait_seconds = float(_os.environ.get("PITH_B200_RING_WAIT_SECONDS", "30"))
-        comm = _peer_comms[key] = PeerRingComm(cp_rank, cp_size, global_ranks, device, group=_peer_group,
+        comm = _peer_comms[key] = PeerRingComm(cp_rank, cp_size, global_ranks, device, group=_peer_group if _peer_group is not None else _ring_groups.get(tuple(global_ranks)),
                                                wait_seconds=wait_seconds)
     return comm
 

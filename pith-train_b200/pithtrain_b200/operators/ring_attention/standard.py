@@ -80,4 +80,5 @@ def ring_attention_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softm
     cp_rank = cp_group.rank()
     cp_size = cp_group.size()
     global_ranks = [dist.distributed_c10d.get_global_rank(cp_group, r) for r in range(cp_size)]
+    _ring.register_group(global_ranks, cp_group)
     return RingAttentionFunc.apply(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, sharding)
