@@ -351,6 +351,18 @@ def main():
         "delta_kernel": (lambda: kernels.bwd_preprocess(out_d, do, delta_d), n_row * Dv * 4 + 4 * n_row),
         "cast_kernel (dQ)": (lambda: kernels.cast_to_bf16(dq_acc), n_row * Dqk * 6),
     }
+    if Dqk == 128:  # the fused q/k RMSNorm + rotary step in front of the operator (head_dim 128 models)
+        w_n = torch.ones(Dqk, dtype=torch.bfloat16, device=dev)
+        pos = torch.arange(S_loc, device=dev, dtype=torch.float32)
+        inv = 1.0 / (1e6 ** (torch.arange(0, Dqk, 2, device=dev, dtype=torch.float32) / Dqk))
+        emb = torch.outer(pos, inv).repeat(1, 2)[None]
+        cos_t, sin_t = emb.cos().bfloat16(), emb.sin().bfloat16()
+        rows_qk = S_loc * (Hq + Hkv) * Dqk
+        hbm_runs["qk_norm_rope_kernel fwd (q, k bf16 -> bf16)"] = (
+            lambda: kernels.qk_norm_rope_fwd(qd, kd, w_n, w_n, cos_t, sin_t, 1e-6), rows_qk * 4 + S_loc * Dqk * 4)
+        hbm_runs["qk_norm_rope_kernel bwd"] = (
+            lambda: kernels.qk_norm_rope_bwd(qd, kd, w_n, w_n, cos_t, sin_t, 1e-6, do if Dv == Dqk else qd, kd),
+            rows_qk * 6 + S_loc * Dqk * 4)
     hbm = {}
     for name, (run, nbytes) in hbm_runs.items():
         for _ in range(3):

@@ -232,6 +232,36 @@ int pith_ipc_open(const void* handle64, void** base);
 int pith_ipc_close(void* base);
 int pith_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 
+typedef struct pith_qk_norm_rope_args {
+  const void* q;            /* [B][S][Hq][128] bf16 (forward input; the backward recomputes from it) */
+  const void* k;            /* [B][S][Hkv][128] bf16 */
+  const void* q_weight;     /* [128] RMSNorm weight of the query heads, weight_dtype */
+  const void* k_weight;     /* [128] */
+  const void* cos;          /* [B][S][128] cs_dtype; a b stride of 0 broadcasts one table over the batch */
+  const void* sin;
+  void* q_out;              /* forward: rotated queries; backward: dL/dq. bf16 [B][S][Hq][128] */
+  void* k_out;              /* forward: rotated keys; backward: dL/dk. bf16 [B][S][Hkv][128] */
+  const void* dq_out;       /* backward only: gradient of the rotated queries, bf16 */
+  const void* dk_out;       /* backward only: gradient of the rotated keys, bf16 */
+  float* dq_weight;         /* backward only: fp32 [128], accumulated into (+=) */
+  float* dk_weight;         /* backward only: fp32 [128], accumulated into (+=) */
+  int32_t B, S, Hq, Hkv, D; /* D must be 128 */
+  int32_t weight_dtype, cs_dtype; /* PITH_DTYPE_* */
+  float eps;
+  int64_t q_stride[3], k_stride[3], q_out_stride[3], k_out_stride[3], dq_out_stride[3], dk_out_stride[3];
+  int64_t cs_stride[2];     /* b, s strides of cos and sin (elements) */
+} pith_qk_norm_rope_args;
+
+/*
+ * Per-head RMSNorm of Q and K followed by rotary position embedding (rotate-half form), in one pass; and its
+ * backward (dL/dq, dL/dk and the two weight gradients) in one pass.
+ * Replace: `self.q_norm(...)`, `self.k_norm(...)` (nn.RMSNorm(head_dim), pithtrain/models/qwen3_30b_a3b.py:381-382,
+ *   :417-418) and `apply_rotary_pos_emb` (:107-136, called at :421), i.e. two normalisation kernels and eight
+ *   elementwise kernels per layer in front of `ring_attention_func` / `flash_attn_func`, and their autograd backward.
+ */
+int pith_qk_norm_rope_fwd(const pith_qk_norm_rope_args* args, void* stream);
+int pith_qk_norm_rope_bwd(const pith_qk_norm_rope_args* args, void* stream);
+
 /* Text of the last host-side rejection on the calling thread. */
 const char* pith_last_error(void);
 /* Human-readable form of a device status word. Returns a pointer to a thread-local buffer. */

@@ -76,6 +76,19 @@ class AttnBwdNoallocArgs(Structure):
     ]
 
 
+class QkNormRopeArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("q_weight", c_void_p), ("k_weight", c_void_p),
+        ("cos", c_void_p), ("sin", c_void_p), ("q_out", c_void_p), ("k_out", c_void_p),
+        ("dq_out", c_void_p), ("dk_out", c_void_p), ("dq_weight", c_void_p), ("dk_weight", c_void_p),
+        ("B", c_int32), ("S", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("D", c_int32),
+        ("weight_dtype", c_int32), ("cs_dtype", c_int32), ("eps", c_float),
+        ("q_stride", I64x3), ("k_stride", I64x3), ("q_out_stride", I64x3), ("k_out_stride", I64x3),
+        ("dq_out_stride", I64x3), ("dk_out_stride", I64x3),
+        ("cs_stride", I64x2),
+    ]
+
+
 NOALLOC_SCRATCH_BYTES = 32 << 20
 FWD_O_FP32 = 1
 BWD_SERIAL = 1
@@ -102,6 +115,8 @@ EXPORTS = {
     "pith_ipc_open": (c_int, [c_void_p, POINTER(c_void_p)]),
     "pith_ipc_close": (c_int, [c_void_p]),
     "pith_peer_copy": (c_int, [c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
+    "pith_qk_norm_rope_fwd": (c_int, [POINTER(QkNormRopeArgs), c_void_p]),
+    "pith_qk_norm_rope_bwd": (c_int, [POINTER(QkNormRopeArgs), c_void_p]),
     "pith_last_error": (c_char_p, []),
     "pith_status_string": (c_char_p, [c_uint32]),
     "pith_abi_version": (c_int, []),

@@ -185,3 +185,62 @@ def combine(out1, lse1, out2, lse2, natural: bool):
     _lib.check(_lib.load().pith_combine(ctypes.byref(a), _stream(out1)), "pith_combine")
     _count(1 if out1.numel() else 0)
     return out, lse
+
+
+def _qk_args(q, k, q_weight, k_weight, cos, sin, eps):
+    _require_cuda(q, k, q_weight, k_weight, cos, sin)
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    if k.shape[0] != B or k.shape[1] != S or k.shape[3] != D:
+        raise ValueError(f"q {tuple(q.shape)} and k {tuple(k.shape)} disagree in batch, sequence or head_dim")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16:
+        raise TypeError("q and k must be bfloat16")
+    dt = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+    if q_weight.dtype not in dt or k_weight.dtype != q_weight.dtype or cos.dtype not in dt or sin.dtype != cos.dtype:
+        raise TypeError("weights and cos/sin must be bfloat16 or float32 (both weights alike, cos and sin alike)")
+    if tuple(q_weight.shape) != (D,) or tuple(k_weight.shape) != (D,) or not (q_weight.is_contiguous()
+                                                                               and k_weight.is_contiguous()):
+        raise ValueError(f"norm weights must be contiguous [{D}]")
+    if cos.dim() != 3 or cos.shape[0] not in (1, B) or cos.shape[1] != S or cos.shape[2] != D or cos.stride(2) != 1 \
+            or sin.shape != cos.shape or sin.stride() != cos.stride():
+        raise ValueError(f"cos/sin must be [B or 1, {S}, {D}] with a contiguous last dimension and equal strides")
+    a = _lib.QkNormRopeArgs()
+    a.q, a.k, a.q_weight, a.k_weight = q.data_ptr(), k.data_ptr(), q_weight.data_ptr(), k_weight.data_ptr()
+    a.cos, a.sin = cos.data_ptr(), sin.data_ptr()
+    a.B, a.S, a.Hq, a.Hkv, a.D = B, S, Hq, Hkv, D
+    a.weight_dtype, a.cs_dtype, a.eps = dt[q_weight.dtype], dt[cos.dtype], float(eps)
+    a.q_stride, a.k_stride = _bshd(q, "q"), _bshd(k, "k")
+    a.cs_stride = I64x2(cos.stride(0) if cos.shape[0] == B and B > 1 else 0, cos.stride(1))
+    return a
+
+
+def qk_norm_rope_fwd(q, k, q_weight, k_weight, cos, sin, eps: float):
+    """Per-head RMSNorm of q and k, then rotary embedding; returns (q_embed, k_embed) bf16 contiguous.
+    See ``pith_qk_norm_rope_fwd``."""
+    a = _qk_args(q, k, q_weight, k_weight, cos, sin, eps)
+    q_out, k_out = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype,
+                                                                                     device=k.device)
+    a.q_out, a.k_out = q_out.data_ptr(), k_out.data_ptr()
+    a.q_out_stride, a.k_out_stride = _bshd(q_out, "q_out"), _bshd(k_out, "k_out")
+    _lib.check(_lib.load().pith_qk_norm_rope_fwd(ctypes.byref(a), _stream(q)), "pith_qk_norm_rope_fwd")
+    _count(1 if q.numel() + k.numel() else 0)
+    return q_out, k_out
+
+
+def qk_norm_rope_bwd(q, k, q_weight, k_weight, cos, sin, eps: float, dq_embed, dk_embed):
+    """Backward of ``qk_norm_rope_fwd``: returns (dq, dk bf16; dq_weight, dk_weight fp32 [D])."""
+    _require_cuda(dq_embed, dk_embed)
+    a = _qk_args(q, k, q_weight, k_weight, cos, sin, eps)
+    if dq_embed.shape != q.shape or dk_embed.shape != k.shape or dq_embed.dtype != torch.bfloat16 \
+            or dk_embed.dtype != torch.bfloat16:
+        raise ValueError("output gradients must be bfloat16 with the shapes of q and k")
+    dq, dk = torch.empty(q.shape, dtype=q.dtype, device=q.device), torch.empty(k.shape, dtype=k.dtype, device=k.device)
+    dw = torch.zeros(2, q.shape[3], dtype=torch.float32, device=q.device)
+    a.q_out, a.k_out = dq.data_ptr(), dk.data_ptr()
+    a.q_out_stride, a.k_out_stride = _bshd(dq, "dq"), _bshd(dk, "dk")
+    a.dq_out, a.dk_out = dq_embed.data_ptr(), dk_embed.data_ptr()
+    a.dq_out_stride, a.dk_out_stride = _bshd(dq_embed, "dq_embed"), _bshd(dk_embed, "dk_embed")
+    a.dq_weight, a.dk_weight = dw[0].data_ptr(), dw[1].data_ptr()
+    _lib.check(_lib.load().pith_qk_norm_rope_bwd(ctypes.byref(a), _stream(q)), "pith_qk_norm_rope_bwd")
+    _count(1 if q.numel() + k.numel() else 0)
+    return dq, dk, dw[0], dw[1]

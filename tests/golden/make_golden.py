@@ -12,7 +12,10 @@ The reference's GPU kernels (flash-attn, Triton) cannot run without a GPU; its C
 are what pin the oracle. ``torch.cuda.get_device_capability`` is stubbed during import because
 pithtrain/operators/mla/__init__.py:3 calls it at import time.
 
-Outputs (small, committed): golden_combine.npz, golden_attention.npz.
+  * pithtrain.models.qwen3_30b_a3b.apply_rotary_pos_emb, Qwen3MoeRotaryEmbedding, with torch.nn.RMSNorm as the
+    model constructs it                                                          (q/k norm + rotary, fwd + autograd)
+
+Outputs (small, committed): golden_combine.npz, golden_attention.npz, golden_qk_norm_rope.npz.
 """
 
 from __future__ import annotations
@@ -86,8 +89,44 @@ def main() -> None:
             f"{name}.meta": np.array([b, s, h, dq, dv, int(causal)], dtype=np.int64),
         })
     np.savez_compressed(HERE / "golden_attention.npz", **cases)
-    for f in ("golden_combine.npz", "golden_attention.npz"):
+    make_qk_norm_rope()
+    for f in ("golden_combine.npz", "golden_attention.npz", "golden_qk_norm_rope.npz"):
         print(f, (HERE / f).stat().st_size, "bytes")
+
+
+def make_qk_norm_rope() -> None:
+    """q/k RMSNorm + rotary embedding exactly as the reference's attention layer runs them
+    (pithtrain/models/qwen3_30b_a3b.py:381-382 modules, :417-421 calls), on CPU: once in fp32 with autograd (pins the
+    oracle) and once in bf16 (the dtype the model runs in; shows the rounding the reference takes between kernels)."""
+    from pithtrain.models.qwen3_30b_a3b import Qwen3MoeRotaryEmbedding, apply_rotary_pos_emb
+    g = torch.Generator().manual_seed(7)
+    B, S, Hq, Hkv, D, eps = 2, 12, 4, 2, 128, 1e-6
+    q = torch.randn(B, S, Hq, D, generator=g).bfloat16().float().requires_grad_()
+    k = (torch.randn(B, S, Hkv, D, generator=g) * 3).bfloat16().float().requires_grad_()
+    q_norm, k_norm = torch.nn.RMSNorm(D, eps=eps), torch.nn.RMSNorm(D, eps=eps)
+    with torch.no_grad():
+        q_norm.weight.copy_((1 + 0.25 * torch.randn(D, generator=g)).bfloat16().float())
+        k_norm.weight.copy_((1 + 0.25 * torch.randn(D, generator=g)).bfloat16().float())
+    position_ids = torch.stack([torch.arange(S) + 5, torch.arange(S) * 37 + 1000])  # [B, S], two different offsets
+    rotary = Qwen3MoeRotaryEmbedding(D, max_position_embeddings=4096)
+    cos, sin = rotary(q, position_ids)
+    qe, ke = apply_rotary_pos_emb(q_norm(q), k_norm(k), cos, sin)
+    dqe = torch.randn(qe.shape, generator=g).bfloat16().float()
+    dke = torch.randn(ke.shape, generator=g).bfloat16().float()
+    torch.autograd.backward([qe, ke], [dqe, dke])
+    with torch.no_grad():  # the same in bf16, as the model runs it
+        qb, kb = q.detach().bfloat16(), k.detach().bfloat16()
+        qn, kn = torch.nn.RMSNorm(D, eps=eps).bfloat16(), torch.nn.RMSNorm(D, eps=eps).bfloat16()
+        qn.weight.copy_(q_norm.weight); kn.weight.copy_(k_norm.weight)
+        cos_b, sin_b = rotary(qb, position_ids)
+        qe_b, ke_b = apply_rotary_pos_emb(qn(qb), kn(kb), cos_b, sin_b)
+    np.savez_compressed(
+        HERE / "golden_qk_norm_rope.npz",
+        q=bits(q), k=bits(k), q_weight=bits(q_norm.weight), k_weight=bits(k_norm.weight),
+        position_ids=position_ids.numpy(), cos=cos.numpy(), sin=sin.numpy(), eps=np.float64(eps),
+        q_embed=qe.detach().numpy(), k_embed=ke.detach().numpy(), dq_embed=bits(dqe), dk_embed=bits(dke),
+        dq=q.grad.numpy(), dk=k.grad.numpy(), dq_weight=q_norm.weight.grad.numpy(), dk_weight=k_norm.weight.grad.numpy(),
+        q_embed_bf16=bits(qe_b), k_embed_bf16=bits(ke_b))
 
 
 if __name__ == "__main__":

@@ -303,3 +303,117 @@ def test_full_size_against_flash_attn(qwen3_full):
     assert_bf16_close(K.cast_to_bf16(f["dq"]), q.grad, "dQ vs flash-attn")
     assert_bf16_close(K.cast_to_bf16(f["dk"]), k.grad, "dK vs flash-attn")
     assert_bf16_close(K.cast_to_bf16(f["dv"]), v.grad, "dV vs flash-attn")
+
+
+# ----------------------------------------------------------------------------- q/k RMSNorm + rotary embedding
+def _qk_golden(dev):
+    import numpy as np
+    from helpers import bf16_from_bits
+    z = np.load(GOLDEN / "golden_qk_norm_rope.npz")
+    t = {k: (bf16_from_bits(z[k]) if z[k].dtype == np.uint16 else torch.from_numpy(np.asarray(z[k])))
+         for k in z.files}
+    return t, float(z["eps"])
+
+
+@pytest.mark.parametrize("w_dtype,cs_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32),
+                                              (torch.float32, torch.bfloat16)])
+def test_qk_norm_rope_golden(cuda_device, w_dtype, cs_dtype):
+    """Forward and backward against what the reference's own modules produced (fp32 on CPU)."""
+    from pithtrain_b200.operators.qk_norm_rope import qk_norm_rope
+    g, eps = _qk_golden(cuda_device)
+    dev = cuda_device
+    q = g["q"].to(dev).requires_grad_()
+    k = g["k"].to(dev).requires_grad_()
+    wq = g["q_weight"].to(dev, w_dtype).requires_grad_()   # bf16-exact values
+    wk = g["k_weight"].to(dev, w_dtype).requires_grad_()
+    cos, sin = g["cos"].to(dev, cs_dtype), g["sin"].to(dev, cs_dtype)
+    qe, ke = qk_norm_rope(q, k, wq, wk, cos, sin, eps)
+    torch.autograd.backward([qe, ke], [g["dq_embed"].to(dev), g["dk_embed"].to(dev)])
+    if cs_dtype == torch.float32:
+        ref = g
+    else:  # bf16 tables: the expected values are the oracle's on the rounded tables
+        from oracle import qk_norm_rope_oracle as R
+        c32, s32 = cos.float().cpu(), sin.float().cpu()
+        args = (g["q"].float(), g["k"].float(), g["q_weight"].float(), g["k_weight"].float(), c32, s32, eps)
+        ref = dict(zip(("q_embed", "k_embed"), R.qk_norm_rope(*args)))
+        ref.update(zip(("dq", "dk", "dq_weight", "dk_weight"),
+                       R.qk_norm_rope_bwd(*args, g["dq_embed"].float(), g["dk_embed"].float())))
+    assert_bf16_close(qe, ref["q_embed"], "q_embed")
+    assert_bf16_close(ke, ref["k_embed"], "k_embed")
+    assert_bf16_close(q.grad, ref["dq"], "dq")
+    assert_bf16_close(k.grad, ref["dk"], "dk")
+    for got, name in ((wq.grad, "dq_weight"), (wk.grad, "dk_weight")):
+        assert got.dtype == w_dtype
+        e = ref[name]
+        assert (got.float().cpu() - e).abs().max() <= 2e-2 + 2.0 ** -7 * e.abs().max(), name
+
+
+def test_qk_norm_rope_full_size_strided(K, cuda_device):
+    """The Qwen3 layer's shape (S = 8192, 32 + 4 heads) with q and k as views of one fused projection output (so
+    their rows are strided) and one cos/sin table broadcast over the batch; checked against the oracle on a slice
+    of positions, plus two size-independent properties: rotation preserves the norm of every row
+    (|z| = |y|), and with unit weights every output row has mean square 1."""
+    from oracle import qk_norm_rope_oracle as R
+    dev = cuda_device
+    B, S, Hq, Hkv, D, eps = 1, 8192, 32, 4, 128, 1e-6
+    gen = torch.Generator().manual_seed(42)
+    qkv = (torch.randn(B, S, (Hq + 2 * Hkv) * D, generator=gen) * 2).bfloat16().to(dev)
+    q = qkv[..., :Hq * D].view(B, S, Hq, D)
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].view(B, S, Hkv, D)
+    wq = (1 + 0.2 * torch.randn(D, generator=gen)).bfloat16().to(dev)
+    wk = (1 + 0.2 * torch.randn(D, generator=gen)).bfloat16().to(dev)
+    cos, sin = (t.bfloat16().to(dev) for t in R.rope_tables(torch.arange(S) + 24576, D))
+    dqe = torch.randn(B, S, Hq, D, generator=gen).bfloat16().to(dev)
+    dke = torch.randn(B, S, Hkv, D, generator=gen).bfloat16().to(dev)
+    qe, ke = K.qk_norm_rope_fwd(q, k, wq, wk, cos, sin, eps)
+    dq, dk, dwq, dwk = K.qk_norm_rope_bwd(q, k, wq, wk, cos, sin, eps, dqe, dke)
+    assert qe.is_contiguous() and ke.is_contiguous()
+    sl = slice(4000, 4128)
+    args = [t.float().cpu() for t in (q[:, sl], k[:, sl], wq, wk, cos[:, sl], sin[:, sl])]
+    rq, rk = R.qk_norm_rope(*args, eps)
+    assert_bf16_close(qe[:, sl], rq, "q_embed slice")
+    assert_bf16_close(ke[:, sl], rk, "k_embed slice")
+    rdq, rdk, _, _ = R.qk_norm_rope_bwd(*args, eps, dqe[:, sl].float().cpu(), dke[:, sl].float().cpu())
+    assert_bf16_close(dq[:, sl], rdq, "dq slice")
+    assert_bf16_close(dk[:, sl], rdk, "dk slice")
+    # weight gradients over ALL rows, against a float64 reduction on the GPU of the same closed form
+    for x, g, w, got in ((q, dqe, wq, dwq), (k, dke, wk, dwk)):
+        x64, g64 = x.double(), g.double()
+        c, s = cos.double().unsqueeze(2), sin.double().unsqueeze(2)
+        t = g64 * s
+        dy = g64 * c + torch.cat((t[..., 64:], -t[..., :64]), dim=-1)
+        xh = x64 * torch.rsqrt(x64.pow(2).mean(-1, keepdim=True) + eps)
+        want = (dy * xh).sum((0, 1, 2))
+        assert (got.double() - want).abs().max() <= 1e-3 * want.abs().max() + 1e-2
+    # properties at full size
+    ones = torch.ones(D, dtype=torch.bfloat16, device=dev)
+    q1, k1 = K.qk_norm_rope_fwd(q, k, ones, ones, cos, sin, eps)
+    for z in (q1, k1):
+        ms = z.float().pow(2).mean(-1)
+        assert (ms - 1).abs().max() < 2e-2          # rotation keeps |y|, and |y|^2 / D = 1 after the norm
+    K.check_device_status(dev)
+
+
+def test_qk_norm_rope_edges(K, cuda_device):
+    """Empty tensors, a row count that is not a multiple of the 16 rows a block handles at a time, zero rows
+    (finite output thanks to eps), and rejected arguments."""
+    dev = cuda_device
+    w = torch.ones(128, dtype=torch.bfloat16, device=dev)
+    cs = torch.ones(1, 0, 128, dtype=torch.bfloat16, device=dev)
+    e = torch.empty(1, 0, 2, 128, dtype=torch.bfloat16, device=dev)
+    qe, ke = K.qk_norm_rope_fwd(e, e, w, w, cs, cs, 1e-6)
+    assert qe.shape == e.shape and ke.shape == e.shape
+    from oracle import qk_norm_rope_oracle as R
+    q = torch.randn(3, 7, 5, 128).bfloat16().to(dev)
+    k = torch.zeros(3, 7, 1, 128, dtype=torch.bfloat16, device=dev)
+    cos, sin = (t.to(dev) for t in R.rope_tables(torch.arange(7), 128))
+    qe, ke = K.qk_norm_rope_fwd(q, k, w, w, cos, sin, 1e-6)
+    rq, _ = R.qk_norm_rope(q.float().cpu(), k.float().cpu(), w.float().cpu(), w.float().cpu(), cos.cpu(), sin.cpu(),
+                           1e-6)
+    assert_bf16_close(qe, rq, "ragged q_embed")
+    assert torch.equal(ke, torch.zeros_like(ke))
+    with pytest.raises(RuntimeError, match="128 only"):
+        K.qk_norm_rope_fwd(q[..., :64].contiguous(), k[..., :64].contiguous(), w[:64].contiguous(),
+                           w[:64].contiguous(), cos[..., :64].contiguous(), sin[..., :64].contiguous(), 1e-6)
+    with pytest.raises(ValueError):
+        K.qk_norm_rope_fwd(q, k, w, w, cos[:, :5], sin[:, :5], 1e-6)

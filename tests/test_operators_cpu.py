@@ -48,6 +48,10 @@ def test_no_cpu_fallback(built_library):
         standard.RingAttentionFunc.apply(q, q, q, 0.1, 0, 1, [0])
     with pytest.raises(NotImplementedError):
         attention.flash_attn_func(q, q, q, dropout_p=0.1)
+    from pithtrain_b200.operators.qk_norm_rope import qk_norm_rope
+    w, cs = torch.ones(128), torch.ones(1, 128, 128)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        qk_norm_rope(q, q, w, w, cs, cs, 1e-6)
 
 
 def test_contiguity_assertion_matches_reference_message():

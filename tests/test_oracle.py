@@ -102,3 +102,54 @@ def test_flop_conventions():
     # Qwen3-30B-A3B attention at S=8192: 5.498e11 forward, x3.5 for forward + backward
     assert abs(O.fwd_flops(1, 32, 8192, 128, 128) - 5.498e11) / 5.498e11 < 1e-3
     assert abs(O.fwd_bwd_flops(1, 32, 8192, 128, 128) - 1.924e12) / 1.924e12 < 1e-3
+
+
+def _golden_qk():
+    from helpers import bf16_from_bits
+    z = np.load(GOLDEN / "golden_qk_norm_rope.npz")
+    t = {k: (bf16_from_bits(z[k]) if z[k].dtype == np.uint16 else torch.from_numpy(np.asarray(z[k])))
+         for k in z.files}
+    t["eps"] = float(z["eps"])
+    return t
+
+
+def test_qk_norm_rope_matches_reference_golden():
+    """The oracle against nn.RMSNorm + the reference's apply_rotary_pos_emb (fp32 on CPU, with autograd), and the
+    oracle's cos/sin tables against Qwen3MoeRotaryEmbedding's."""
+    from oracle import qk_norm_rope_oracle as R
+    g = _golden_qk()
+    q, k, wq, wk = (g[x].float() for x in ("q", "k", "q_weight", "k_weight"))
+    qe, ke = R.qk_norm_rope(q, k, wq, wk, g["cos"], g["sin"], g["eps"])
+    assert torch.allclose(qe, g["q_embed"], rtol=1e-5, atol=2e-6)
+    assert torch.allclose(ke, g["k_embed"], rtol=1e-5, atol=2e-6)
+    dq, dk, dwq, dwk = R.qk_norm_rope_bwd(q, k, wq, wk, g["cos"], g["sin"], g["eps"], g["dq_embed"].float(),
+                                          g["dk_embed"].float())
+    for got, name in ((dq, "dq"), (dk, "dk"), (dwq, "dq_weight"), (dwk, "dk_weight")):
+        assert torch.allclose(got, g[name], rtol=1e-4, atol=2e-5), name
+    for b in range(2):
+        cos, sin = R.rope_tables(g["position_ids"][b], 128)
+        assert torch.allclose(cos[0], g["cos"][b], atol=1e-6) and torch.allclose(sin[0], g["sin"][b], atol=1e-6)
+    # the reference's own bf16 flow (a rounding after every elementwise kernel) stays within bf16 rounding of it
+    assert (g["q_embed_bf16"].float() - qe).abs().max() <= 3 * 2.0 ** -8 * qe.abs().max()
+    assert (g["k_embed_bf16"].float() - ke).abs().max() <= 3 * 2.0 ** -8 * ke.abs().max()
+
+
+def test_qk_norm_rope_backward_formula():
+    """The closed form the CUDA backward uses (dy = dz*cos + rotate_half^T(dz*sin); dx = r*(g - xhat*mean(g*xhat)),
+    g = dy*w; dw = sum dy*xhat) against autograd through the oracle, in fp64."""
+    from oracle import qk_norm_rope_oracle as R
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 5, 3, 128, generator=gen, dtype=torch.float64)
+    w = 1 + 0.3 * torch.randn(128, generator=gen, dtype=torch.float64)
+    cos, sin = R.rope_tables(torch.arange(5) * 11, 128, dtype=torch.float64)
+    dz = torch.randn(x.shape, generator=gen, dtype=torch.float64)
+    dx_ref, _, dw_ref, _ = R.qk_norm_rope_bwd(x, x, w, w, cos, sin, 1e-6, dz, torch.zeros_like(dz))
+    c, s = cos.unsqueeze(2), sin.unsqueeze(2)
+    t = dz * s
+    dy = dz * c + torch.cat((t[..., 64:], -t[..., :64]), dim=-1)
+    r = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+    xh = x * r
+    g = dy * w
+    dx = r * (g - xh * (g * xh).mean(-1, keepdim=True))
+    assert torch.allclose(dx, dx_ref, rtol=1e-10, atol=1e-12)
+    assert torch.allclose((dy * xh).sum((0, 1, 2)), dw_ref, rtol=1e-10, atol=1e-12)
