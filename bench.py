@@ -241,10 +241,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(run, steps, in_flight=None, finish=None):
-        """Device time of `steps` calls of run(), max over ranks, in ms per call."""
+    def timed(run, steps, in_flight=None, finish=None, queue_ahead=False):
+        """Device time of `steps` calls of run(), max over ranks, in ms per call.
+
+        queue_ahead (single kernels only): a spin kernel of a few ms runs first, so that the host has enqueued all
+        launches before the first one starts and the events bracket GPU execution, not Python call overhead."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if queue_ahead:
+            torch.cuda._sleep(int(6e6))
         e0.record()
         for _ in range(steps):
             run()
@@ -328,7 +333,7 @@ def main():
     for name, (run, mult) in runs.items():
         for _ in range(3):
             run()
-        kms = timed(run, 10)
+        kms = timed(run, 10, queue_ahead=True)
         kern[name] = {"ms": kms, "tflops": mult * fwd_fl_local / (kms * 1e-3) / 1e12}
     dom = max(kern, key=lambda n: kern[n]["ms"])
     roofline = {
@@ -367,7 +372,7 @@ def main():
     for name, (run, nbytes) in hbm_runs.items():
         for _ in range(3):
             run()
-        kms = timed(run, 10)
+        kms = timed(run, 10, queue_ahead=True)
         hbm[name] = {"us": kms * 1e3, "gbs": nbytes / (kms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (kms * 1e-3) / 1e9 / pk["hbm_gbs"]}
     roofline["hbm_kernels"] = hbm
 

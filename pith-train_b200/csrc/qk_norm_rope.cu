@@ -5,8 +5,9 @@
 //   z[i]      = y[i]      * cos[i]      - y[i + 64] * sin[i]           i < 64
 //   z[i + 64] = y[i + 64] * cos[i + 64] + y[i]      * sin[i + 64]
 //
-// Sixteen lanes own one row (8 consecutive elements each, 16-byte accesses); the rotate-half partner of lane j is
-// lane j ^ 8 and the row reductions are four shuffles. Q rows and K rows go through the same launch. cos/sin are
+// Sixteen lanes own one row; lane j holds elements [4j, 4j+4) and [64+4j, 64+4j+4), i.e. both members of four
+// rotate-half pairs (8-byte accesses, 128 contiguous bytes per half row), so only the two row reductions need
+// shuffles (four each). Q rows and K rows go through the same launch. cos/sin are
 // shared by all heads of a position, so they come from L1/L2 after the first head. All arithmetic is fp32 with a
 // single rounding to bf16 at the end. The backward recomputes the row statistics from x instead of saving them.
 #include "../../include/pith_b200.h"
@@ -29,9 +30,11 @@ struct QkParams {
   int64_t cs[2];                          // b, s strides of cos / sin (elements)
 };
 
-__device__ __forceinline__ void load8_bf16(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+// Elements [off, off + 4) and [off + 64, off + 68) of a row: a lane's two halves of the rotate-half pairs.
+__device__ __forceinline__ void load_pair_bf16(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint2 lo = __ldg(reinterpret_cast<const uint2*>(p));
+  const uint2 hi = __ldg(reinterpret_cast<const uint2*>(p + 64));
+  const uint32_t w[4] = {lo.x, lo.y, hi.x, hi.y};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     v[2 * i] = __uint_as_float(w[i] << 16);
@@ -40,114 +43,139 @@ __device__ __forceinline__ void load8_bf16(const __nv_bfloat16* p, float (&v)[8]
 }
 
 template <bool F32>
-__device__ __forceinline__ void load8_any(const void* base, int64_t off, float (&v)[8]) {
+__device__ __forceinline__ void load_pair_any(const void* base, int64_t off, float (&v)[8]) {
   if constexpr (F32) {
-    const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(base) + off);
-    const float4 a = __ldg(p), b = __ldg(p + 1);
+    const float* p = static_cast<const float*>(base) + off;
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 64));
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
   } else {
-    load8_bf16(static_cast<const __nv_bfloat16*>(base) + off, v);
+    load_pair_bf16(static_cast<const __nv_bfloat16*>(base) + off, v);
   }
 }
 
-__device__ __forceinline__ void store8_bf16(__nv_bfloat16* p, const float (&v)[8]) {
-  uint4 u;
-  u.x = pack_bf16(v[0], v[1]); u.y = pack_bf16(v[2], v[3]); u.z = pack_bf16(v[4], v[5]); u.w = pack_bf16(v[6], v[7]);
-  *reinterpret_cast<uint4*>(p) = u;
+__device__ __forceinline__ void store_pair_bf16(__nv_bfloat16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+  *reinterpret_cast<uint2*>(p + 64) = make_uint2(pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
 }
 
-__device__ __forceinline__ float sum16(float v) {  // over the 16 lanes that share a row
-  v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
-  v += __shfl_xor_sync(0xFFFFFFFFu, v, 4);
-  v += __shfl_xor_sync(0xFFFFFFFFu, v, 2);
-  v += __shfl_xor_sync(0xFFFFFFFFu, v, 1);
+__device__ __forceinline__ float sum16(float v, uint32_t mask) {  // over the 16 lanes that share a row
+  v += __shfl_xor_sync(mask, v, 8);
+  v += __shfl_xor_sync(mask, v, 4);
+  v += __shfl_xor_sync(mask, v, 2);
+  v += __shfl_xor_sync(mask, v, 1);
   return v;
 }
 
-template <bool BWD, bool W_F32, bool CS_F32>
-__global__ void __launch_bounds__(256) qk_norm_rope_kernel(const QkParams p) {
-  __shared__ float dw_s[2][128];
+constexpr int kHeadChunk = 8;  // heads of one position that a half-warp walks through with one cos/sin load
+
+// v[0..4) are elements d0..d0+3 of the row, v[4..8) elements d0+64..d0+67: both members of four rotate-half pairs.
+// blockIdx.y is the batch entry; blockIdx.z selects a chunk of kHeadChunk heads, first those of Q, then those of K.
+// Each half-warp takes positions s = blockIdx.x * 16 + its index, + 16 * gridDim.x, ...; per position it loads
+// cos/sin once and walks through the chunk's heads G rows at a time. The two half-warps of a warp shuffle under
+// their own masks, so one may run out of positions before the other.
+#ifndef PITH_QK_G_FWD
+#define PITH_QK_G_FWD 4
+#endif
+#ifndef PITH_QK_G_BWD
+#define PITH_QK_G_BWD 1
+#endif
+#ifndef PITH_QK_MINB_FWD
+#define PITH_QK_MINB_FWD 3
+#endif
+#ifndef PITH_QK_MINB_BWD
+#define PITH_QK_MINB_BWD 3
+#endif
+
+template <bool BWD, bool W_F32, bool CS_F32, int G>
+__global__ void __launch_bounds__(256, BWD ? PITH_QK_MINB_BWD : PITH_QK_MINB_FWD) qk_norm_rope_kernel(const QkParams p) {
+  __shared__ float dw_s[128];
+  const int qchunks = (p.Hq + kHeadChunk - 1) / kHeadChunk;
+  const int z = static_cast<int>(blockIdx.z) >= qchunks ? 1 : 0, b = blockIdx.y;
+  const int hbeg = (static_cast<int>(blockIdx.z) - (z ? qchunks : 0)) * kHeadChunk;
+  const int nh = min(kHeadChunk, (z ? p.Hkv : p.Hq) - hbeg);
   const uint32_t tid = threadIdx.x, lane16 = tid & 15u;
-  const bool upper = lane16 >= 8u;  // this lane owns elements of the second half of the row
-  const uint32_t htot = static_cast<uint32_t>(p.Hq + p.Hkv);
-  const uint32_t items = static_cast<uint32_t>(p.S) * htot;  // rows of one batch entry
-  const uint32_t stride = gridDim.x * 16u;
-  const uint32_t first = (blockIdx.x * 256u + tid) >> 4;
-  const uint32_t trips = (items + stride - 1u) / stride;  // the same for every lane: the shuffles need whole warps
-  const int b = blockIdx.y;
-  const int d0 = static_cast<int>(lane16) * 8;
+  const uint32_t mask = 0xFFFFu << (tid & 16u);
+  const int d0 = static_cast<int>(lane16) * 4;
+  const int64_t x_s = p.xs[z][1], x_h = p.xs[z][2], o_s = p.os[z][1], o_h = p.os[z][2];
+  const int64_t g_s = p.dzs[z][1], g_h = p.dzs[z][2];
+  const __nv_bfloat16* xb = p.x[z] + b * p.xs[z][0] + hbeg * x_h + d0;
+  __nv_bfloat16* ob = p.out[z] + b * p.os[z][0] + hbeg * o_h + d0;
+  const __nv_bfloat16* gb = BWD ? p.dz[z] + b * p.dzs[z][0] + hbeg * g_h + d0 : nullptr;
+  const int64_t cs_b = b * p.cs[0] + d0;
 
-  float w[2][8];
-  load8_any<W_F32>(p.w[0], d0, w[0]);
-  load8_any<W_F32>(p.w[1], d0, w[1]);
-  float dw[2][8] = {};
+  float w[8], dw[8] = {};
+  load_pair_any<W_F32>(p.w[z], d0, w);
   if constexpr (BWD) {
-    dw_s[tid >> 7][tid & 127u] = 0.f;
+    if (tid < 128u) dw_s[tid] = 0.f;
     __syncthreads();
   }
 
-  for (uint32_t t = 0; t < trips; ++t) {
-    const uint32_t item = first + t * stride;
-    const bool valid = item < items;
-    const uint32_t s = valid ? item / htot : 0u;
-    const uint32_t hh = valid ? item - s * htot : 0u;
-    const int which = hh >= static_cast<uint32_t>(p.Hq) ? 1 : 0;
-    const int h = static_cast<int>(hh) - (which ? p.Hq : 0);
-    float x[8] = {}, c[8] = {}, sn[8] = {}, g[8] = {};
-    if (valid) {
-      load8_bf16(p.x[which] + b * p.xs[which][0] + s * p.xs[which][1] + h * p.xs[which][2] + d0, x);
-      const int64_t co = b * p.cs[0] + s * p.cs[1] + d0;
-      load8_any<CS_F32>(p.cos, co, c);
-      load8_any<CS_F32>(p.sin, co, sn);
-      if constexpr (BWD)
-        load8_bf16(p.dz[which] + b * p.dzs[which][0] + s * p.dzs[which][1] + h * p.dzs[which][2] + d0, g);
-    }
-    float ss = 0.f;
+  for (int s = static_cast<int>(blockIdx.x * 16u + (tid >> 4)); s < p.S; s += static_cast<int>(gridDim.x) * 16) {
+    float c[8], sn[8];
+    const int64_t co = cs_b + s * p.cs[1];
+    load_pair_any<CS_F32>(p.cos, co, c);
+    load_pair_any<CS_F32>(p.sin, co, sn);
+    const __nv_bfloat16* xp = xb + s * x_s;
+    __nv_bfloat16* op = ob + s * o_s;
+    const __nv_bfloat16* gp = BWD ? gb + s * g_s : nullptr;
+#pragma unroll(BWD ? 1 : 2)  // the backward holds twice the state per row: unrolled it spills
+    for (int h = 0; h < nh; h += G) {
+      float x[G][8], g[BWD ? G : 1][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
-    const float r = rsqrtf(sum16(ss) * (1.f / 128.f) + p.eps);
-    float res[8], wv[8];  // selects instead of indexing by `which`: keeps the arrays in registers
-#pragma unroll
-    for (int i = 0; i < 8; ++i) wv[i] = which ? w[1][i] : w[0][i];
-    if constexpr (!BWD) {
-      float y[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) y[i] = x[i] * r * wv[i];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float partner = __shfl_xor_sync(0xFFFFFFFFu, y[i], 8);
-        res[i] = fmaf(y[i], c[i], (upper ? partner : -partner) * sn[i]);
+      for (int j = 0; j < G; ++j) {
+        const int hj = min(h + j, nh - 1);  // a short last group re-reads its last head; only h + j < nh is stored
+        load_pair_bf16(xp + hj * x_h, x[j]);
+        if constexpr (BWD) load_pair_bf16(gp + hj * g_h, g[j]);
       }
-    } else {
-      // dy = dz * cos + rotate_half^T(dz * sin): the partner's dz * sin comes back with the opposite sign
-      float gx = 0.f, dy[8], xh[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float partner = __shfl_xor_sync(0xFFFFFFFFu, g[i] * sn[i], 8);
-        dy[i] = fmaf(g[i], c[i], upper ? -partner : partner);
-        xh[i] = x[i] * r;
-        const float dwi = dy[i] * xh[i];
-        dw[0][i] += which ? 0.f : dwi;
-        dw[1][i] += which ? dwi : 0.f;
-        dy[i] *= wv[i];
-        gx = fmaf(dy[i], xh[i], gx);
+      for (int j = 0; j < G; ++j) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss = fmaf(x[j][i], x[j][i], ss);
+        const float r = rsqrtf(sum16(ss, mask) * (1.f / 128.f) + p.eps);
+        float res[8];
+        if constexpr (!BWD) {
+          float y[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[i] = x[j][i] * (r * w[i]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            res[i] = fmaf(y[i], c[i], -y[i + 4] * sn[i]);
+            res[i + 4] = fmaf(y[i + 4], c[i + 4], y[i] * sn[i + 4]);
+          }
+        } else {
+          // dy = dz * cos + rotate_half^T(dz * sin): the pair partner's dz * sin comes back with the opposite sign
+          float gx = 0.f, dy[8], xh[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dy[i] = fmaf(g[j][i], c[i], g[j][i + 4] * sn[i + 4]);
+            dy[i + 4] = fmaf(g[j][i + 4], c[i + 4], -g[j][i] * sn[i]);
+          }
+          const bool counted = h + j < nh;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            xh[i] = x[j][i] * r;
+            dw[i] = fmaf(counted ? dy[i] : 0.f, xh[i], dw[i]);
+            dy[i] *= w[i];
+            gx = fmaf(dy[i], xh[i], gx);
+          }
+          const float m = sum16(gx, mask) * (1.f / 128.f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) res[i] = r * (dy[i] - xh[i] * m);
+        }
+        if (h + j < nh) store_pair_bf16(op + (h + j) * o_h, res);
       }
-      const float m = sum16(gx) * (1.f / 128.f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) res[i] = r * (dy[i] - xh[i] * m);
     }
-    if (valid)
-      store8_bf16(p.out[which] + b * p.os[which][0] + s * p.os[which][1] + h * p.os[which][2] + d0, res);
   }
 
   if constexpr (BWD) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      atomicAdd(&dw_s[0][d0 + i], dw[0][i]);
-      atomicAdd(&dw_s[1][d0 + i], dw[1][i]);
+    for (int i = 0; i < 4; ++i) {
+      atomicAdd(&dw_s[d0 + i], dw[i]);
+      atomicAdd(&dw_s[d0 + 64 + i], dw[i + 4]);
     }
     __syncthreads();
-    atomicAdd(p.dw[tid >> 7] + (tid & 127u), dw_s[tid >> 7][tid & 127u]);
+    if (tid < 128u) atomicAdd(p.dw[z] + tid, dw_s[tid]);
   }
 }
 
@@ -161,7 +189,6 @@ static int launch(const pith_qk_norm_rope_args* a, void* stream) {
   PITH_REQUIRE(a->B >= 0 && a->S >= 0 && a->Hq >= 0 && a->Hkv >= 0, "negative size");
   PITH_REQUIRE(a->D == 128, "head_dim %d is not supported (128 only)", a->D);
   if (a->B == 0 || a->S == 0 || a->Hq + a->Hkv == 0) return kOk;
-  PITH_REQUIRE(static_cast<int64_t>(a->S) * (a->Hq + a->Hkv) < (1ll << 31), "S * (Hq + Hkv) exceeds 2^31");
   PITH_REQUIRE(a->B <= 65535, "B exceeds 65535");
   PITH_REQUIRE(a->q_weight && a->k_weight && a->cos && a->sin, "null weight or cos/sin pointer");
   PITH_REQUIRE(aligned16(a->q_weight) && aligned16(a->k_weight) && aligned16(a->cos) && aligned16(a->sin),
@@ -200,25 +227,29 @@ static int launch(const pith_qk_norm_rope_args* a, void* stream) {
   p.cos = a->cos; p.sin = a->sin;
   p.B = a->B; p.S = a->S; p.Hq = a->Hq; p.Hkv = a->Hkv; p.eps = a->eps;
   p.cs[0] = a->cs_stride[0]; p.cs[1] = a->cs_stride[1];
-  const int64_t items = static_cast<int64_t>(a->S) * (a->Hq + a->Hkv);
+  constexpr int G = BWD ? PITH_QK_G_BWD : PITH_QK_G_FWD;  // rows a thread has in flight
+  const int chunks = (a->Hq + kHeadChunk - 1) / kHeadChunk + (a->Hkv + kHeadChunk - 1) / kHeadChunk;
+  PITH_REQUIRE(chunks <= 65535, "too many heads");
   int sms = 148;
   {
     int dev = 0;
     PITH_CUDA(cudaGetDevice(&dev));
     PITH_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
-  // 8 resident CTAs per SM over all batch entries; never more CTAs than there are 16-row groups
-  int64_t gx = (static_cast<int64_t>(sms) * 8 + a->B - 1) / a->B;
-  const int64_t need = (items + 15) / 16;
+  // 16 positions per CTA and pass; about 16 CTAs per SM over all batch entries and head chunks, never more than
+  // there are groups of 16 positions
+  int64_t gx = (static_cast<int64_t>(sms) * 16 + static_cast<int64_t>(a->B) * chunks - 1) /
+               (static_cast<int64_t>(a->B) * chunks);
+  const int64_t need = (static_cast<int64_t>(a->S) + 15) / 16;
   if (gx > need) gx = need;
   if (gx < 1) gx = 1;
-  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(a->B));
+  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(a->B), static_cast<unsigned>(chunks));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool wf = a->weight_dtype == PITH_DTYPE_F32, cf = a->cs_dtype == PITH_DTYPE_F32;
-  if (wf && cf) qk_norm_rope_kernel<BWD, true, true><<<grid, 256, 0, st>>>(p);
-  else if (wf) qk_norm_rope_kernel<BWD, true, false><<<grid, 256, 0, st>>>(p);
-  else if (cf) qk_norm_rope_kernel<BWD, false, true><<<grid, 256, 0, st>>>(p);
-  else qk_norm_rope_kernel<BWD, false, false><<<grid, 256, 0, st>>>(p);
+  if (wf && cf) qk_norm_rope_kernel<BWD, true, true, G><<<grid, 256, 0, st>>>(p);
+  else if (wf) qk_norm_rope_kernel<BWD, true, false, G><<<grid, 256, 0, st>>>(p);
+  else if (cf) qk_norm_rope_kernel<BWD, false, true, G><<<grid, 256, 0, st>>>(p);
+  else qk_norm_rope_kernel<BWD, false, false, G><<<grid, 256, 0, st>>>(p);
   PITH_CUDA(cudaGetLastError());
   return kOk;
 }

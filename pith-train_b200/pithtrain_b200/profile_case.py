@@ -3,7 +3,7 @@
     python -m pithtrain_b200.profile_case [--shape qwen3|mla] [--seq 8192] [--repeat 2]
 
 Launch order per repeat: attn_fwd_kernel, delta_kernel, attn_bwd_kernel<kDkDv>, attn_bwd_kernel<kDq>,
-3 x cast_kernel, combine_kernel. The working set (a few hundred MB) is larger than the 126 MB L2 and far below the
+3 x cast_kernel, combine_kernel, and (head_dim 128) qk_norm_rope_kernel forward and backward. The working set (a few hundred MB) is larger than the 126 MB L2 and far below the
 sizes at which a multi-pass profiler capture gets slow. Prints the CUDA-event time of each launch.
 """
 
@@ -38,6 +38,11 @@ def main() -> None:
     dq, dk, dv = (torch.zeros(t.shape, dtype=torch.float32, device=dev) for t in (q, k, v))
     acc = torch.randn(1, S, hq, 128, device=dev)
 
+    w_norm = torch.ones(dqk, dtype=torch.bfloat16, device=dev)
+    emb = torch.outer(torch.arange(S, dtype=torch.float32),
+                      1.0 / (1e6 ** (torch.arange(0, dqk, 2, dtype=torch.float32) / dqk))).repeat(1, 2)[None]
+    cos, sin = emb.cos().bfloat16().to(dev), emb.sin().bfloat16().to(dev)
+
     def timed(name, fn):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -54,6 +59,9 @@ def main() -> None:
         timed("attn_bwd_kernel<kDq>", lambda: K.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, dq, None, None))
         timed("cast_kernel x3", lambda: (K.cast_to_bf16(dq), K.cast_to_bf16(dk), K.cast_to_bf16(dv)))
         timed("combine_kernel", lambda: K.combine(acc, lse, out, lse, natural=False))
+        if dqk == 128:
+            timed("qk_norm_rope_kernel fwd", lambda: K.qk_norm_rope_fwd(q, k, w_norm, w_norm, cos, sin, 1e-6))
+            timed("qk_norm_rope_kernel bwd", lambda: K.qk_norm_rope_bwd(q, k, w_norm, w_norm, cos, sin, 1e-6, do, k))
     K.check_device_status(dev)
 
 
