@@ -368,6 +368,17 @@ def main():
         hbm_runs["qk_norm_rope_kernel bwd"] = (
             lambda: kernels.qk_norm_rope_bwd(qd, kd, w_n, w_n, cos_t, sin_t, 1e-6, do if Dv == Dqk else qd, kd),
             rows_qk * 6 + S_loc * Dqk * 4)
+    if Dqk == 192:  # the rotary + input assembly step in front of the MLA operator
+        q_in = torch.randn(1, S_loc, Hq, 192, device=dev).bfloat16()
+        kv_in = torch.randn(1, S_loc, Hq, 256, device=dev).bfloat16()
+        kpe_in = torch.randn(1, S_loc, 64, device=dev).bfloat16()
+        ang = torch.outer(torch.arange(S_loc, device=dev, dtype=torch.float32),
+                          1.0 / (1e4 ** (torch.arange(0, 64, 2, device=dev, dtype=torch.float32) / 64))).repeat(1, 2)[None]
+        cos_m, sin_m = ang.cos().bfloat16(), ang.sin().bfloat16()
+        asm_bytes = S_loc * (Hq * (192 + 256 + 192 + 192 + 128) * 2 + 64 * 2 + 64 * 4)
+        hbm_runs["mla_assemble_kernel fwd"] = (lambda: kernels.mla_assemble_fwd(q_in, kv_in, kpe_in, cos_m, sin_m),
+                                               asm_bytes)
+        hbm_runs["mla_assemble_kernel bwd"] = (lambda: kernels.mla_assemble_bwd(cos_m, sin_m, qd, kd, vd), asm_bytes)
     hbm = {}
     for name, (run, nbytes) in hbm_runs.items():
         for _ in range(3):

@@ -262,6 +262,42 @@ typedef struct pith_qk_norm_rope_args {
 int pith_qk_norm_rope_fwd(const pith_qk_norm_rope_args* args, void* stream);
 int pith_qk_norm_rope_bwd(const pith_qk_norm_rope_args* args, void* stream);
 
+typedef struct pith_mla_assemble_args {
+  /* forward inputs */
+  const void* q;       /* [B][S][H][192] bf16: q_nope (128) | q_pe (64, interleaved rotary pairs) */
+  const void* kv;      /* [B][S][H][256] bf16: k_nope (128) | v (128) */
+  const void* k_pe;    /* [B][S][64] bf16: the one rotary key of a position, shared by all heads */
+  const void* cos;     /* [B][S][64] cs_dtype, already gathered by position; a b stride of 0 broadcasts */
+  const void* sin;
+  /* forward outputs */
+  void* query;         /* [B][S][H][192] bf16 */
+  void* key;           /* [B][S][H][192] bf16 */
+  void* value;         /* [B][S][H][128] bf16 */
+  /* backward inputs (gradients of query / key / value; same strides as the forward outputs) */
+  const void* dquery;
+  const void* dkey;
+  const void* dvalue;
+  /* backward outputs (same strides as q / kv / k_pe) */
+  void* dq;
+  void* dkv;
+  void* dk_pe;
+  int32_t B, S, H;
+  int32_t Dnope, Drope, Dv;  /* must be 128, 64, 128 */
+  int32_t cs_dtype;          /* PITH_DTYPE_* */
+  int64_t q_stride[3], kv_stride[3], query_stride[3], key_stride[3], value_stride[3]; /* b, s, h (elements) */
+  int64_t k_pe_stride[2], cs_stride[2];                                                /* b, s (elements) */
+} pith_mla_assemble_args;
+
+/*
+ * Rotary embedding of the rope parts of Q and K (DeepSeek form) and assembly of the MLA operator's inputs, in one
+ * pass; and the backward of it (dk_pe sums over the heads) in one pass.
+ * Replace: `apply_rotary_pos_emb` (pithtrain/models/deepseek_v2_lite.py:173-187, called at :446), the four slice
+ *   assignments into `new_empty` tensors (:448-454) and `value_states.contiguous()` (:463, :468) in front of
+ *   `ring_mla_attention_func` / `MLA`, with their autograd backward.
+ */
+int pith_mla_assemble_fwd(const pith_mla_assemble_args* args, void* stream);
+int pith_mla_assemble_bwd(const pith_mla_assemble_args* args, void* stream);
+
 /* Text of the last host-side rejection on the calling thread. */
 const char* pith_last_error(void);
 /* Human-readable form of a device status word. Returns a pointer to a thread-local buffer. */

@@ -89,6 +89,20 @@ class QkNormRopeArgs(Structure):
     ]
 
 
+class MlaAssembleArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("kv", c_void_p), ("k_pe", c_void_p), ("cos", c_void_p), ("sin", c_void_p),
+        ("query", c_void_p), ("key", c_void_p), ("value", c_void_p),
+        ("dquery", c_void_p), ("dkey", c_void_p), ("dvalue", c_void_p),
+        ("dq", c_void_p), ("dkv", c_void_p), ("dk_pe", c_void_p),
+        ("B", c_int32), ("S", c_int32), ("H", c_int32),
+        ("Dnope", c_int32), ("Drope", c_int32), ("Dv", c_int32), ("cs_dtype", c_int32),
+        ("q_stride", I64x3), ("kv_stride", I64x3), ("query_stride", I64x3), ("key_stride", I64x3),
+        ("value_stride", I64x3),
+        ("k_pe_stride", I64x2), ("cs_stride", I64x2),
+    ]
+
+
 NOALLOC_SCRATCH_BYTES = 32 << 20
 FWD_O_FP32 = 1
 BWD_SERIAL = 1
@@ -117,6 +131,8 @@ EXPORTS = {
     "pith_peer_copy": (c_int, [c_void_p, c_void_p, ctypes.c_size_t, c_void_p]),
     "pith_qk_norm_rope_fwd": (c_int, [POINTER(QkNormRopeArgs), c_void_p]),
     "pith_qk_norm_rope_bwd": (c_int, [POINTER(QkNormRopeArgs), c_void_p]),
+    "pith_mla_assemble_fwd": (c_int, [POINTER(MlaAssembleArgs), c_void_p]),
+    "pith_mla_assemble_bwd": (c_int, [POINTER(MlaAssembleArgs), c_void_p]),
     "pith_last_error": (c_char_p, []),
     "pith_status_string": (c_char_p, [c_uint32]),
     "pith_abi_version": (c_int, []),

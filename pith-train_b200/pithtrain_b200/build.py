@@ -21,7 +21,7 @@ BUILD_DIR = CSRC_DIR / "build"
 LIB_PATH = Path(os.environ.get("PITH_B200_LIB", PKG_DIR / "libpith_b200.so"))
 
 SOURCES = ["host_common.cu", "elementwise.cu", "attn_fwd.cu", "attn_bwd.cu", "attn_bwd128.cu", "noalloc.cu", "peer.cu",
-           "qk_norm_rope.cu"]
+           "qk_norm_rope.cu", "mla_assemble.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

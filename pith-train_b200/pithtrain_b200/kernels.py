@@ -244,3 +244,68 @@ def qk_norm_rope_bwd(q, k, q_weight, k_weight, cos, sin, eps: float, dq_embed, d
     _lib.check(_lib.load().pith_qk_norm_rope_bwd(ctypes.byref(a), _stream(q)), "pith_qk_norm_rope_bwd")
     _count(1 if q.numel() + k.numel() else 0)
     return dq, dk, dw[0], dw[1]
+
+
+def _mla_asm_args(B, S, H, cos, sin):
+    _require_cuda(cos, sin)
+    dt = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+    if cos.dtype not in dt or sin.dtype != cos.dtype:
+        raise TypeError("cos and sin must both be bfloat16 or float32")
+    if cos.dim() != 3 or cos.shape[0] not in (1, B) or tuple(cos.shape[1:]) != (S, 64) or cos.stride(2) != 1 \
+            or sin.shape != cos.shape or sin.stride() != cos.stride():
+        raise ValueError(f"cos/sin must be [B or 1, {S}, 64] (gathered by position) with equal strides")
+    a = _lib.MlaAssembleArgs()
+    a.cos, a.sin = cos.data_ptr(), sin.data_ptr()
+    a.B, a.S, a.H, a.Dnope, a.Drope, a.Dv, a.cs_dtype = B, S, H, 128, 64, 128, dt[cos.dtype]
+    a.cs_stride = I64x2(cos.stride(0) if cos.shape[0] == B and B > 1 else 0, cos.stride(1))
+    return a
+
+
+def mla_assemble_fwd(q, kv, k_pe, cos, sin):
+    """(query [B,S,H,192], key [B,S,H,192], value [B,S,H,128]) from q = [q_nope | q_pe], kv = [k_nope | v] and the
+    per-position rotary key k_pe; see ``pith_mla_assemble_fwd``."""
+    _require_cuda(q, kv, k_pe)
+    if q.dim() != 4 or q.shape[3] != 192 or tuple(kv.shape) != (*q.shape[:3], 256):
+        raise ValueError(f"q must be [B,S,H,192] and kv [B,S,H,256], got {tuple(q.shape)} and {tuple(kv.shape)}")
+    B, S, H, _ = q.shape
+    if k_pe.dim() == 4 and k_pe.shape[2] == 1:
+        k_pe = k_pe[:, :, 0]
+    if tuple(k_pe.shape) != (B, S, 64) or k_pe.stride(2) != 1:
+        raise ValueError(f"k_pe must be [B,S,64] or [B,S,1,64] with a contiguous last dimension, got {tuple(k_pe.shape)}")
+    if not (q.dtype == kv.dtype == k_pe.dtype == torch.bfloat16):
+        raise TypeError("q, kv and k_pe must be bfloat16")
+    a = _mla_asm_args(B, S, H, cos, sin)
+    query, key = (torch.empty((B, S, H, 192), dtype=q.dtype, device=q.device) for _ in range(2))
+    value = torch.empty((B, S, H, 128), dtype=q.dtype, device=q.device)
+    a.q, a.kv, a.k_pe = q.data_ptr(), kv.data_ptr(), k_pe.data_ptr()
+    a.query, a.key, a.value = query.data_ptr(), key.data_ptr(), value.data_ptr()
+    a.q_stride, a.kv_stride = _bshd(q, "q"), _bshd(kv, "kv")
+    a.query_stride, a.key_stride, a.value_stride = _bshd(query, "query"), _bshd(key, "key"), _bshd(value, "value")
+    a.k_pe_stride = I64x2(k_pe.stride(0), k_pe.stride(1))
+    _lib.check(_lib.load().pith_mla_assemble_fwd(ctypes.byref(a), _stream(q)), "pith_mla_assemble_fwd")
+    _count(1 if q.numel() else 0)
+    return query, key, value
+
+
+def mla_assemble_bwd(cos, sin, dquery, dkey, dvalue):
+    """Gradients (dq [B,S,H,192], dkv [B,S,H,256], dk_pe [B,S,64]; contiguous) from the gradients of
+    query / key / value; see ``pith_mla_assemble_bwd``."""
+    _require_cuda(dquery, dkey, dvalue)
+    if dquery.dim() != 4 or dquery.shape[3] != 192:
+        raise ValueError(f"dquery must be [B,S,H,192], got {tuple(dquery.shape)}")
+    B, S, H, _ = dquery.shape
+    for t, d, n in ((dquery, 192, "dquery"), (dkey, 192, "dkey"), (dvalue, 128, "dvalue")):
+        if tuple(t.shape) != (B, S, H, d) or t.dtype != torch.bfloat16:
+            raise ValueError(f"{n} must be bfloat16 [{B},{S},{H},{d}]")
+    a = _mla_asm_args(B, S, H, cos, sin)
+    dq = torch.empty((B, S, H, 192), dtype=torch.bfloat16, device=dquery.device)
+    dkv = torch.empty((B, S, H, 256), dtype=torch.bfloat16, device=dquery.device)
+    dk_pe = torch.empty((B, S, 64), dtype=torch.bfloat16, device=dquery.device)
+    a.dq, a.dkv, a.dk_pe = dq.data_ptr(), dkv.data_ptr(), dk_pe.data_ptr()
+    a.dquery, a.dkey, a.dvalue = dquery.data_ptr(), dkey.data_ptr(), dvalue.data_ptr()
+    a.q_stride, a.kv_stride = _bshd(dq, "dq"), _bshd(dkv, "dkv")
+    a.query_stride, a.key_stride, a.value_stride = _bshd(dquery, "dquery"), _bshd(dkey, "dkey"), _bshd(dvalue, "dvalue")
+    a.k_pe_stride = I64x2(dk_pe.stride(0), dk_pe.stride(1))
+    _lib.check(_lib.load().pith_mla_assemble_bwd(ctypes.byref(a), _stream(dquery)), "pith_mla_assemble_bwd")
+    _count(1 if dq.numel() else 0)
+    return dq, dkv, dk_pe

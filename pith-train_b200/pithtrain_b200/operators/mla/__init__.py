@@ -77,4 +77,6 @@ def _mla_bwd_dq(q, k, v, dout, lse, delta, softmax_scale: float, causal: bool = 
     return K.cast_to_bf16(dq)
 
 
-__all__ = ["MLA", "_mla_fwd", "_mla_bwd_preprocess", "_mla_bwd_dk_dv", "_mla_bwd_dq"]
+from .assemble import MLAAssembleFunc, mla_assemble  # noqa: E402
+
+__all__ = ["MLA", "_mla_fwd", "_mla_bwd_preprocess", "_mla_bwd_dk_dv", "_mla_bwd_dq", "MLAAssembleFunc", "mla_assemble"]

@@ -15,7 +15,11 @@ pithtrain/operators/mla/__init__.py:3 calls it at import time.
   * pithtrain.models.qwen3_30b_a3b.apply_rotary_pos_emb, Qwen3MoeRotaryEmbedding, with torch.nn.RMSNorm as the
     model constructs it                                                          (q/k norm + rotary, fwd + autograd)
 
-Outputs (small, committed): golden_combine.npz, golden_attention.npz, golden_qk_norm_rope.npz.
+  * pithtrain.models.deepseek_v2_lite.apply_rotary_pos_emb, DeepseekV2LiteYarnRotaryEmbedding
+                                                              (MLA rotary + input assembly, fwd + autograd)
+
+Outputs (small, committed): golden_combine.npz, golden_attention.npz, golden_qk_norm_rope.npz,
+golden_mla_assemble.npz.
 """
 
 from __future__ import annotations
@@ -90,8 +94,45 @@ def main() -> None:
         })
     np.savez_compressed(HERE / "golden_attention.npz", **cases)
     make_qk_norm_rope()
-    for f in ("golden_combine.npz", "golden_attention.npz", "golden_qk_norm_rope.npz"):
+    make_mla_assemble()
+    for f in ("golden_combine.npz", "golden_attention.npz", "golden_qk_norm_rope.npz", "golden_mla_assemble.npz"):
         print(f, (HERE / f).stat().st_size, "bytes")
+
+
+def make_mla_assemble() -> None:
+    """Rotary embedding + assembly of the MLA operator's inputs with the reference's own ``apply_rotary_pos_emb``
+    and ``DeepseekV2LiteYarnRotaryEmbedding`` (pithtrain/models/deepseek_v2_lite.py:173-187, :103-163), following
+    the statements of the attention layer's forward (:426-454, :463) one by one, on CPU in fp32 with autograd."""
+    from pithtrain.models.deepseek_v2_lite import DeepseekV2LiteYarnRotaryEmbedding, apply_rotary_pos_emb
+    g = torch.Generator().manual_seed(11)
+    B, S, H = 2, 10, 3
+    q = torch.randn(B, S, H, 192, generator=g).bfloat16().float().requires_grad_()
+    kv = torch.randn(B, S, H, 256, generator=g).bfloat16().float().requires_grad_()
+    k_pe = torch.randn(B, S, 1, 64, generator=g).bfloat16().float().requires_grad_()
+    position_ids = torch.stack([torch.arange(S) + 3, torch.arange(S) * 29 + 500])
+    rotary = DeepseekV2LiteYarnRotaryEmbedding(64, max_position_embeddings=2048, scaling_factor=40.0, base=10000,
+                                               original_max_position_embeddings=4096, beta_fast=32, beta_slow=1,
+                                               mscale=0.707, mscale_all_dim=0.707)
+    q_nope, q_pe = torch.split(q, [128, 64], dim=-1)
+    k_nope, value_states = torch.split(kv, [128, 128], dim=-1)
+    cos, sin = rotary(value_states, seq_len=int(position_ids.max()) + 1)
+    q_rot, k_rot = apply_rotary_pos_emb(q_pe, k_pe, cos, sin, position_ids, unsqueeze_dim=2)
+    query_states = k_rot.new_empty(B, S, H, 192)
+    query_states[:, :, :, :128] = q_nope
+    query_states[:, :, :, 128:] = q_rot
+    key_states = k_rot.new_empty(B, S, H, 192)
+    key_states[:, :, :, :128] = k_nope
+    key_states[:, :, :, 128:] = k_rot
+    value = value_states.contiguous()
+    grads = [torch.randn(t.shape, generator=g).bfloat16().float() for t in (query_states, key_states, value)]
+    torch.autograd.backward([query_states, key_states, value], grads)
+    np.savez_compressed(
+        HERE / "golden_mla_assemble.npz",
+        q=bits(q), kv=bits(kv), k_pe=bits(k_pe[:, :, 0]), position_ids=position_ids.numpy(),
+        cos=cos[position_ids].detach().float().numpy(), sin=sin[position_ids].detach().float().numpy(),
+        query=query_states.detach().numpy(), key=key_states.detach().numpy(), value=value.detach().numpy(),
+        dquery=bits(grads[0]), dkey=bits(grads[1]), dvalue=bits(grads[2]),
+        dq=q.grad.numpy(), dkv=kv.grad.numpy(), dk_pe=k_pe.grad[:, :, 0].numpy())
 
 
 def make_qk_norm_rope() -> None:

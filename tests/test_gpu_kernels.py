@@ -417,3 +417,94 @@ def test_qk_norm_rope_edges(K, cuda_device):
                            w[:64].contiguous(), cos[..., :64].contiguous(), sin[..., :64].contiguous(), 1e-6)
     with pytest.raises(ValueError):
         K.qk_norm_rope_fwd(q, k, w, w, cos[:, :5], sin[:, :5], 1e-6)
+
+
+# ----------------------------------------------------------------------------- MLA rotary + input assembly
+@pytest.mark.parametrize("cs_dtype", [torch.float32, torch.bfloat16])
+def test_mla_assemble_golden(cuda_device, cs_dtype):
+    """Forward and backward against what the reference's own functions produced (fp32 on CPU)."""
+    import numpy as np
+    from helpers import bf16_from_bits
+    from oracle import mla_assemble_oracle as M
+    from pithtrain_b200.operators.mla import mla_assemble
+    z = np.load(GOLDEN / "golden_mla_assemble.npz")
+    g = {k: (bf16_from_bits(z[k]) if z[k].dtype == np.uint16 else torch.from_numpy(np.asarray(z[k]))) for k in z.files}
+    dev = cuda_device
+    q, kv = g["q"].to(dev).requires_grad_(), g["kv"].to(dev).requires_grad_()
+    k_pe = g["k_pe"].to(dev).unsqueeze(2).requires_grad_()           # [B,S,1,64] as the layer has it
+    cos, sin = g["cos"].to(dev, cs_dtype), g["sin"].to(dev, cs_dtype)
+    query, key, value = mla_assemble(q, kv, k_pe, cos, sin)
+    torch.autograd.backward([query, key, value], [g[n].to(dev) for n in ("dquery", "dkey", "dvalue")])
+    if cs_dtype == torch.float32:
+        ref = g
+    else:
+        args = (g["q"].float(), g["kv"].float(), g["k_pe"].float(), cos.float().cpu(), sin.float().cpu())
+        ref = dict(zip(("query", "key", "value"), M.mla_assemble(*args)))
+        ref.update(zip(("dq", "dkv", "dk_pe"), M.mla_assemble_bwd(*args, g["dquery"].float(), g["dkey"].float(),
+                                                                  g["dvalue"].float())))
+    assert_bf16_close(query, ref["query"], "query")
+    assert_bf16_close(key, ref["key"], "key")
+    assert torch.equal(value.cpu(), g["kv"][..., 128:])               # a pure copy: bit-exact
+    assert torch.equal(query[..., :128].cpu(), g["q"][..., :128])
+    assert torch.equal(key[..., :128].cpu(), g["kv"][..., :128])
+    assert_bf16_close(q.grad, ref["dq"], "dq")
+    assert_bf16_close(kv.grad, ref["dkv"], "dkv")
+    assert k_pe.grad.shape == k_pe.shape
+    assert_bf16_close(k_pe.grad[:, :, 0], ref["dk_pe"], "dk_pe")
+
+
+def test_mla_assemble_full_size(K, cuda_device):
+    """DeepSeek-V2-Lite's shape at 4096 tokens per rank with strided inputs (q and kv as views of wider projection
+    outputs, k_pe as the tail of the compressed-kv projection), the rotary tables given with position_ids as the
+    reference passes them; oracle on a slice, plus: rotation preserves the norm of every rope row, the rope part of
+    key is the same for all heads, and dk_pe equals the head-sum property (zero dkey rope part -> zero dk_pe)."""
+    from oracle import mla_assemble_oracle as M
+    from pithtrain_b200.operators.mla import mla_assemble
+    dev = cuda_device
+    B, S, H = 1, 4096, 16
+    gen = torch.Generator().manual_seed(5)
+    qbuf = torch.randn(B, S, H * 192 + 64, generator=gen).bfloat16().to(dev)
+    kvbuf = torch.randn(B, S, H * 256, generator=gen).bfloat16().to(dev)
+    ckv = torch.randn(B, S, 512 + 64, generator=gen).bfloat16().to(dev)
+    q = qbuf[..., :H * 192].view(B, S, H, 192)
+    kv = kvbuf.view(B, S, H, 256)
+    k_pe = ckv[..., 512:].view(B, S, 1, 64)
+    pos = torch.arange(S, device=dev).view(1, S) + 28672
+    inv = 1.0 / (10000 ** (torch.arange(0, 64, 2, dtype=torch.float32, device=dev) / 64))
+    emb = torch.outer(torch.arange(32768, dtype=torch.float32, device=dev), inv).repeat(1, 2)
+    cos_t, sin_t = (emb.cos() * 1.1).bfloat16(), (emb.sin() * 1.1).bfloat16()
+    query, key, value = mla_assemble(q, kv, k_pe, cos_t, sin_t, pos)
+    assert query.is_contiguous() and key.is_contiguous() and value.is_contiguous()
+    sl = slice(1000, 1064)
+    cos_g, sin_g = cos_t[pos][:, sl].float().cpu(), sin_t[pos][:, sl].float().cpu()
+    rq, rk, rv = M.mla_assemble(q[:, sl].float().cpu(), kv[:, sl].float().cpu(), k_pe[:, sl, 0].float().cpu(), cos_g, sin_g)
+    assert_bf16_close(query[:, sl], rq, "query slice")
+    assert_bf16_close(key[:, sl], rk, "key slice")
+    assert torch.equal(value.cpu(), kv[..., 128:].cpu())
+    assert torch.equal(key[..., 128:], key[:, :, :1, 128:].expand(-1, -1, H, -1))
+    # |rope(x)|^2 = 1.1^2 |x|^2 up to bf16 rounding of the tables and the outputs
+    n_in = q[..., 128:].float().pow(2).sum(-1)
+    n_out = query[..., 128:].float().pow(2).sum(-1)
+    assert ((n_out / n_in).sqrt() - 1.1).abs().max() < 2e-2
+    dquery = torch.randn(B, S, H, 192, generator=gen).bfloat16().to(dev)
+    dkey = torch.randn(B, S, H, 192, generator=gen).bfloat16().to(dev)
+    dvalue = torch.randn(B, S, H, 128, generator=gen).bfloat16().to(dev)
+    dq, dkv, dk_pe = K.mla_assemble_bwd(cos_t[pos], sin_t[pos], dquery, dkey, dvalue)
+    rdq, rdkv, rdkpe = M.mla_assemble_bwd(q[:, sl].float().cpu(), kv[:, sl].float().cpu(), k_pe[:, sl, 0].float().cpu(),
+                                          cos_g, sin_g, dquery[:, sl].float().cpu(), dkey[:, sl].float().cpu(),
+                                          dvalue[:, sl].float().cpu())
+    assert_bf16_close(dq[:, sl], rdq, "dq slice")
+    assert_bf16_close(dkv[:, sl], rdkv, "dkv slice")
+    assert_bf16_close(dk_pe[:, sl], rdkpe, "dk_pe slice")
+    dkey0 = dkey.clone()
+    dkey0[..., 128:] = 0
+    assert not K.mla_assemble_bwd(cos_t[pos], sin_t[pos], dquery, dkey0, dvalue)[2].any()
+    # empty input and rejected sizes
+    e = torch.empty(1, 0, H, 192, dtype=torch.bfloat16, device=dev)
+    out = K.mla_assemble_fwd(e, torch.empty(1, 0, H, 256, dtype=torch.bfloat16, device=dev),
+                             torch.empty(1, 0, 64, dtype=torch.bfloat16, device=dev),
+                             torch.empty(1, 0, 64, device=dev), torch.empty(1, 0, 64, device=dev))
+    assert out[0].shape == (1, 0, H, 192)
+    with pytest.raises(ValueError):
+        K.mla_assemble_fwd(q[..., :128], kv, k_pe, cos_t[pos], sin_t[pos])
+    K.check_device_status(dev)

@@ -52,6 +52,10 @@ def test_no_cpu_fallback(built_library):
     w, cs = torch.ones(128), torch.ones(1, 128, 128)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         qk_norm_rope(q, q, w, w, cs, cs, 1e-6)
+    from pithtrain_b200.operators.mla import mla_assemble
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        mla_assemble(torch.zeros(1, 8, 2, 192, dtype=torch.bfloat16), torch.zeros(1, 8, 2, 256, dtype=torch.bfloat16),
+                     torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16), torch.ones(1, 8, 64), torch.ones(1, 8, 64))
 
 
 def test_contiguity_assertion_matches_reference_message():

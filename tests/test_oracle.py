@@ -153,3 +153,25 @@ def test_qk_norm_rope_backward_formula():
     dx = r * (g - xh * (g * xh).mean(-1, keepdim=True))
     assert torch.allclose(dx, dx_ref, rtol=1e-10, atol=1e-12)
     assert torch.allclose((dy * xh).sum((0, 1, 2)), dw_ref, rtol=1e-10, atol=1e-12)
+
+
+def _golden_npz(name):
+    from helpers import bf16_from_bits
+    z = np.load(GOLDEN / name)
+    return {k: (bf16_from_bits(z[k]) if z[k].dtype == np.uint16 else torch.from_numpy(np.asarray(z[k])))
+            for k in z.files}
+
+
+def test_mla_assemble_matches_reference_golden():
+    """The oracle against the reference's apply_rotary_pos_emb (DeepSeek form) + the layer's assembly statements,
+    fp32 on CPU with autograd."""
+    from oracle import mla_assemble_oracle as M
+    g = _golden_npz("golden_mla_assemble.npz")
+    q, kv, k_pe = g["q"].float(), g["kv"].float(), g["k_pe"].float()
+    query, key, value = M.mla_assemble(q, kv, k_pe, g["cos"], g["sin"])
+    for got, name in ((query, "query"), (key, "key"), (value, "value")):
+        assert torch.allclose(got, g[name], rtol=1e-6, atol=1e-6), name
+    grads = M.mla_assemble_bwd(q, kv, k_pe, g["cos"], g["sin"], g["dquery"].float(), g["dkey"].float(),
+                               g["dvalue"].float())
+    for got, name in zip(grads, ("dq", "dkv", "dk_pe")):
+        assert torch.allclose(got, g[name], rtol=1e-5, atol=1e-5), name
