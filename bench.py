@@ -323,10 +323,11 @@ def main():
     dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=dev)
     dq_acc = torch.zeros(q.shape, dtype=torch.float32, device=dev)
     qd, kd, vd = q.detach(), k.detach(), v.detach()
+    bwd_label = " (attn_bwd128_kernel at head_dim 128)" if Dqk == 128 else " (Dqk = 192 instantiation)"
     runs = {
         "attn_fwd_kernel": (lambda: kernels.attn_fwd(qd, kd, vd, scale, True, 0, out=out_d, lse=lse_d), 1.0),
-        "attn_bwd_kernel<kDkDv> (attn_bwd128_kernel at head_dim 128)": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, None, dk_acc, dv_acc), 2.0),
-        "attn_bwd_kernel<kDq> (attn_bwd128_kernel at head_dim 128)": (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, dq_acc, None, None), 0.5),
+        "attn_bwd_kernel<kDkDv>" + bwd_label: (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, None, dk_acc, dv_acc), 2.0),
+        "attn_bwd_kernel<kDq>" + bwd_label: (lambda: kernels.attn_bwd(qd, kd, vd, do, lse_d, delta_d, scale, True, 0, dq_acc, None, None), 0.5),
     }
     kern = {}
     fwd_fl_local = float(Hq) * S_loc * S_loc * (Dqk + Dv)  # causal forward FLOPs of the local block

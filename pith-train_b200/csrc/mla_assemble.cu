@@ -12,9 +12,10 @@
 // out[32+j] = x[2j+1] cos[32+j] + x[2j] sin[32+j]  (j < 32): both outputs depend on one interleaved input pair, so a
 // lane that holds 8 consecutive inputs (4 pairs) produces outputs [4l, 4l+4) and [32+4l, 32+4l+4) on its own.
 //
-// One warp per position walks through the heads: lanes 0-15 move the 128 "nope" elements of Q (and dQ), lanes 16-23
-// rotate the 64 rope elements; all 32 lanes move the 256-element kv row; the rotated k_pe is computed once per
-// position (lanes 24-31) and stored for every head.
+// One warp per position walks through the heads (the forward through a chunk of four; blockIdx.z picks the chunk):
+// lanes 0-15 move the 128 "nope" elements of Q (and dQ), lanes 16-23 rotate the 64 rope elements; all 32 lanes move
+// the 256-element kv row; the rotated k_pe is computed once per position and chunk (lanes 24-31) and stored for
+// every head.
 #include "../../include/pith_b200.h"
 #include "common.cuh"
 #include "host_common.h"
@@ -87,6 +88,8 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   return make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
 }
 
+constexpr int kFwdHeads = 4;  // heads per work item (blockIdx.z picks the chunk)
+
 template <bool BWD, bool CS_F32>
 __global__ void __launch_bounds__(256) mla_assemble_kernel(const MlaAsmParams p) {
   const uint32_t lane = threadIdx.x & 31u;
@@ -117,20 +120,29 @@ __global__ void __launch_bounds__(256) mla_assemble_kernel(const MlaAsmParams p)
         klo = pack4(lo);
         khi = pack4(hi);
       }
-      for (int h = 0; h < p.H; ++h) {
-        const __nv_bfloat16* qh = qrow + h * p.qs[2];
-        const __nv_bfloat16* kvh = kvrow + h * p.kvs[2];
+      // the forward splits the heads over blockIdx.z in chunks of kFwdHeads; all loads of a chunk are issued first
+      const int hbeg = static_cast<int>(blockIdx.z) * kFwdHeads;
+      uint4 kvv[kFwdHeads], qv[kFwdHeads];
+#pragma unroll
+      for (int j = 0; j < kFwdHeads; ++j) {
+        const int h = min(hbeg + j, p.H - 1);
+        kvv[j] = __ldg(reinterpret_cast<const uint4*>(kvrow + h * p.kvs[2]) + lane);
+        qv[j] = lane < 24u ? __ldg(reinterpret_cast<const uint4*>(qrow + h * p.qs[2]) + lane) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < kFwdHeads; ++j) {
+        const int h = hbeg + j;
+        if (h >= p.H) break;
         __nv_bfloat16* qy = qyrow + h * p.qys[2];
         __nv_bfloat16* ky = kyrow + h * p.kys[2];
-        const uint4 kvv = __ldg(reinterpret_cast<const uint4*>(kvh) + lane);
         if (lane < 16u) {
-          *(reinterpret_cast<uint4*>(qy) + lane) = __ldg(reinterpret_cast<const uint4*>(qh) + lane);
-          *(reinterpret_cast<uint4*>(ky) + lane) = kvv;
+          *(reinterpret_cast<uint4*>(qy) + lane) = qv[j];
+          *(reinterpret_cast<uint4*>(ky) + lane) = kvv[j];
         } else {
-          *(reinterpret_cast<uint4*>(vrow + h * p.vs[2]) + (lane - 16u)) = kvv;
+          *(reinterpret_cast<uint4*>(vrow + h * p.vs[2]) + (lane - 16u)) = kvv[j];
           if (rope_q) {
             float x[8], lo[4], hi[4];
-            unpack8(__ldg(reinterpret_cast<const uint4*>(qh) + lane), x);
+            unpack8(qv[j], x);
             rope_fwd(x, cl, sl, ch, sh, lo, hi);
             *reinterpret_cast<uint2*>(qy + 128 + 4 * l8) = pack4(lo);
             *reinterpret_cast<uint2*>(qy + 160 + 4 * l8) = pack4(hi);
@@ -141,36 +153,53 @@ __global__ void __launch_bounds__(256) mla_assemble_kernel(const MlaAsmParams p)
         }
       }
     } else {
-      float klo[4] = {}, khi[4] = {};  // sum over heads of the rope part of dkey (lanes 24-31)
-      for (int h = 0; h < p.H; ++h) {
-        __nv_bfloat16* qh = qrow + h * p.qs[2];      // dq (output)
-        __nv_bfloat16* kvh = kvrow + h * p.kvs[2];   // dkv (output)
+      // Like the forward: a chunk of kFwdHeads heads per blockIdx.z, loads first. The rope part of dkey is summed
+      // over ALL heads by lanes 24-31 of chunk 0 only (16 x 128 bytes per position), which then write dk_pe.
+      const int hbeg = static_cast<int>(blockIdx.z) * kFwdHeads;
+      uint4 a[kFwdHeads], c[kFwdHeads];  // lanes 0-15: dquery nope, dkey nope; lanes 16-31: rope source, dvalue
+#pragma unroll
+      for (int j = 0; j < kFwdHeads; ++j) {
+        const int h = min(hbeg + j, p.H - 1);
         const __nv_bfloat16* qy = qyrow + h * p.qys[2];
         const __nv_bfloat16* ky = kyrow + h * p.kys[2];
         if (lane < 16u) {
-          *(reinterpret_cast<uint4*>(qh) + lane) = __ldg(reinterpret_cast<const uint4*>(qy) + lane);
-          *(reinterpret_cast<uint4*>(kvh) + lane) = __ldg(reinterpret_cast<const uint4*>(ky) + lane);
+          a[j] = __ldg(reinterpret_cast<const uint4*>(qy) + lane);
+          c[j] = __ldg(reinterpret_cast<const uint4*>(ky) + lane);
         } else {
-          *(reinterpret_cast<uint4*>(kvh) + lane) =
-              __ldg(reinterpret_cast<const uint4*>(vrow + h * p.vs[2]) + (lane - 16u));
-          const __nv_bfloat16* src = rope_q ? qy : ky;
-          float lo[4], hi[4];
-          load4<false>(src, 128 + 4 * l8, lo);
-          load4<false>(src, 160 + 4 * l8, hi);
-          if (rope_q) {
-            float dx[8];
-            rope_bwd(lo, hi, cl, sl, ch, sh, dx);
-            *(reinterpret_cast<uint4*>(qh) + lane) = pack8(dx);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              klo[i] += lo[i];
-              khi[i] += hi[i];
-            }
-          }
+          const uint2 lo = __ldg(reinterpret_cast<const uint2*>(qy + 128 + 4 * l8));
+          const uint2 hi = __ldg(reinterpret_cast<const uint2*>(qy + 160 + 4 * l8));
+          a[j] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+          c[j] = __ldg(reinterpret_cast<const uint4*>(vrow + h * p.vs[2]) + (lane - 16u));
         }
       }
-      if (rope_k) {
+#pragma unroll
+      for (int j = 0; j < kFwdHeads; ++j) {
+        const int h = hbeg + j;
+        if (h >= p.H) break;
+        __nv_bfloat16* qh = qrow + h * p.qs[2];     // dq (output)
+        __nv_bfloat16* kvh = kvrow + h * p.kvs[2];  // dkv (output)
+        *(reinterpret_cast<uint4*>(kvh) + lane) = c[j];
+        if (lane < 16u) {
+          *(reinterpret_cast<uint4*>(qh) + lane) = a[j];
+        } else if (rope_q) {
+          float g[8], lo[4], hi[4], dx[8];
+          unpack8(a[j], g);  // g[0..4) = gradient of outputs 4l..4l+3, g[4..8) = of outputs 32+4l..
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { lo[i] = g[i]; hi[i] = g[4 + i]; }
+          rope_bwd(lo, hi, cl, sl, ch, sh, dx);
+          *(reinterpret_cast<uint4*>(qh) + lane) = pack8(dx);
+        }
+      }
+      if (rope_k && blockIdx.z == 0) {
+        float klo[4] = {}, khi[4] = {};
+#pragma unroll 4
+        for (int h = 0; h < p.H; ++h) {
+          float lo[4], hi[4];
+          load4<false>(kyrow + h * p.kys[2], 128 + 4 * l8, lo);
+          load4<false>(kyrow + h * p.kys[2], 160 + 4 * l8, hi);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { klo[i] += lo[i]; khi[i] += hi[i]; }
+        }
         float dx[8];
         rope_bwd(klo, khi, cl, sl, ch, sh, dx);
         *reinterpret_cast<uint4*>(kpe) = pack8(dx);
@@ -225,11 +254,14 @@ static int launch_mla_assemble(const pith_mla_assemble_args* a, void* stream) {
     PITH_CUDA(cudaGetDevice(&dev));
     PITH_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
-  // 8 positions per CTA and pass; about 8 CTAs per SM over all batch entries
-  int64_t gx = (static_cast<int64_t>(sms) * 8 + a->B - 1) / a->B;
+  // 8 positions per CTA and pass; about 16 CTAs per SM over all batch entries and head chunks
+  const int chunks = (a->H + kFwdHeads - 1) / kFwdHeads;
+  PITH_REQUIRE(chunks <= 65535, "too many heads");
+  int64_t gx = (static_cast<int64_t>(sms) * 16 + static_cast<int64_t>(a->B) * chunks - 1) /
+               (static_cast<int64_t>(a->B) * chunks);
   const int64_t need = (static_cast<int64_t>(a->S) + 7) / 8;
   if (gx > need) gx = need;
-  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(a->B));
+  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(a->B), static_cast<unsigned>(chunks));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->cs_dtype == PITH_DTYPE_F32) mla_assemble_kernel<BWD, true><<<grid, 256, 0, st>>>(p);
   else mla_assemble_kernel<BWD, false><<<grid, 256, 0, st>>>(p);

@@ -495,7 +495,8 @@ def test_mla_assemble_full_size(K, cuda_device):
                                           dvalue[:, sl].float().cpu())
     assert_bf16_close(dq[:, sl], rdq, "dq slice")
     assert_bf16_close(dkv[:, sl], rdkv, "dkv slice")
-    assert_bf16_close(dk_pe[:, sl], rdkpe, "dk_pe slice")
+    # dk_pe sums 16 heads: its entries are ~4x larger, so its share of bf16 rounding in the mean is too
+    assert_bf16_close(dk_pe[:, sl], rdkpe, "dk_pe slice", mean_abs=2e-3 + 2.0 ** -9 * rdkpe.abs().mean().item())
     dkey0 = dkey.clone()
     dkey0[..., 128:] = 0
     assert not K.mla_assemble_bwd(cos_t[pos], sin_t[pos], dquery, dkey0, dvalue)[2].any()
