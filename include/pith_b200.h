@@ -207,7 +207,7 @@ size_t pith_attn_bwd_noalloc_scratch_bytes(int32_t B, int32_t Sq, int32_t Sk, in
  *   then stores the new *counter into `flag` (which may be mapped memory of a peer GPU).
  * pith_flag_wait: in stream order, ++*counter (local memory), then `stream` waits until the LOCAL `flag` reaches
  *   *counter (wrap-safe). The wait gives up after about `max_seconds` (at most 120), records code 3 in *status and
- *   lets the stream continue.
+ *   lets the stream continue; while *status is non-zero every later wait returns at once.
  * pith_enable_peer_access: enables direct access from the current device to `peer_device` (idempotent).
  */
 int pith_flag_signal(uint32_t* flag, uint32_t* counter, void* stream);

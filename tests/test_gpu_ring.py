@@ -168,6 +168,11 @@ def test_flag_wait_is_bounded_and_reports(cuda_device):
     word = status.item() & 0xFFFFFFFF
     assert word >> 24 == 3 and (word & 0xFFFFFF) == 1
     assert b"neighbour" in lib.pith_status_string(word)
+    t0 = time.perf_counter()  # with the status word set, later waits return at once (counters still advance)
+    for _ in range(20):
+        _lib.check(lib.pith_flag_wait(flag.data_ptr() + 4, ctr.data_ptr() + 8, 0.2, status.data_ptr(), s), "wait")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0 and ctr[2].item() == 21
     assert lib.pith_flag_wait(0, ctr.data_ptr(), 0.2, 0, s) != 0  # null flag rejected on the host
     assert lib.pith_flag_wait(flag.data_ptr(), ctr.data_ptr(), 1e9, 0, s) != 0  # unbounded wait rejected
     assert torch.ones(4, device=cuda_device).sum().item() == 4.0
