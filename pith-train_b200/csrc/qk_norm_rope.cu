@@ -31,15 +31,28 @@ struct QkParams {
 };
 
 // Elements [off, off + 4) and [off + 64, off + 68) of a row: a lane's two halves of the rotate-half pairs.
-__device__ __forceinline__ void load_pair_bf16(const __nv_bfloat16* p, float (&v)[8]) {
+__device__ __forceinline__ uint4 load_pair_raw(const __nv_bfloat16* p) {
   const uint2 lo = __ldg(reinterpret_cast<const uint2*>(p));
   const uint2 hi = __ldg(reinterpret_cast<const uint2*>(p + 64));
-  const uint32_t w[4] = {lo.x, lo.y, hi.x, hi.y};
+  return make_uint4(lo.x, lo.y, hi.x, hi.y);
+}
+
+__device__ __forceinline__ void unpack_pair(const uint4 u, float (&v)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     v[2 * i] = __uint_as_float(w[i] << 16);
     v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
   }
+}
+
+__device__ __forceinline__ void load_pair_bf16(const __nv_bfloat16* p, float (&v)[8]) { unpack_pair(load_pair_raw(p), v); }
+
+// The same as packed f32x2 pairs: V[0], V[1] = the four elements of the first half, V[2], V[3] = of the second half.
+__device__ __forceinline__ void unpack_pair2(const uint4 u, uint64_t (&V)[4]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) V[i] = f2_pack(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
 }
 
 template <bool F32>
@@ -103,71 +116,105 @@ __global__ void __launch_bounds__(256, BWD ? PITH_QK_MINB_BWD : PITH_QK_MINB_FWD
   const __nv_bfloat16* gb = BWD ? p.dz[z] + b * p.dzs[z][0] + hbeg * g_h + d0 : nullptr;
   const int64_t cs_b = b * p.cs[0] + d0;
 
-  float w[8], dw[8] = {};
+  float w[8], dw[8];
   load_pair_any<W_F32>(p.w[z], d0, w);
   if constexpr (BWD) {
     if (tid < 128u) dw_s[tid] = 0.f;
     __syncthreads();
   }
 
+  // Packed pairs (fma/mul.rn.f32x2): index 0, 1 = the lane's four elements of the first half of the row, 2, 3 = its
+  // four elements of the second half; pair q of the first half rotates with pair q + 2.
+  uint64_t W[4], DW[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) W[q] = f2_pack(w[2 * q], w[2 * q + 1]);
+
   for (int s = static_cast<int>(blockIdx.x * 16u + (tid >> 4)); s < p.S; s += static_cast<int>(gridDim.x) * 16) {
-    float c[8], sn[8];
-    const int64_t co = cs_b + s * p.cs[1];
-    load_pair_any<CS_F32>(p.cos, co, c);
-    load_pair_any<CS_F32>(p.sin, co, sn);
+    uint64_t C[4], S[4], NS[2];
+    {
+      float c[8], sn[8];
+      const int64_t co = cs_b + s * p.cs[1];
+      load_pair_any<CS_F32>(p.cos, co, c);
+      load_pair_any<CS_F32>(p.sin, co, sn);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        C[q] = f2_pack(c[2 * q], c[2 * q + 1]);
+        S[q] = f2_pack(sn[2 * q], sn[2 * q + 1]);
+      }
+      NS[0] = f2_pack(-sn[0], -sn[1]);
+      NS[1] = f2_pack(-sn[2], -sn[3]);
+    }
     const __nv_bfloat16* xp = xb + s * x_s;
     __nv_bfloat16* op = ob + s * o_s;
     const __nv_bfloat16* gp = BWD ? gb + s * g_s : nullptr;
 #pragma unroll(BWD ? 1 : 2)  // the backward holds twice the state per row: unrolled it spills
     for (int h = 0; h < nh; h += G) {
-      float x[G][8], g[BWD ? G : 1][8];
+      uint4 xr[G], gr[BWD ? G : 1];  // raw bf16 words of G rows: all loads are in flight before the first use
 #pragma unroll
       for (int j = 0; j < G; ++j) {
         const int hj = min(h + j, nh - 1);  // a short last group re-reads its last head; only h + j < nh is stored
-        load_pair_bf16(xp + hj * x_h, x[j]);
-        if constexpr (BWD) load_pair_bf16(gp + hj * g_h, g[j]);
+        xr[j] = load_pair_raw(xp + hj * x_h);
+        if constexpr (BWD) gr[j] = load_pair_raw(gp + hj * g_h);
       }
 #pragma unroll
       for (int j = 0; j < G; ++j) {
-        float ss = 0.f;
+        uint64_t X[4], R4[4];
+        unpack_pair2(xr[j], X);
+        uint64_t acc = f2_mul(X[0], X[0]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(x[j][i], x[j][i], ss);
-        const float r = rsqrtf(sum16(ss, mask) * (1.f / 128.f) + p.eps);
-        float res[8];
+        for (int q = 1; q < 4; ++q) acc = f2_fma(X[q], X[q], acc);
+        float s0, s1;
+        f2_unpack(acc, s0, s1);
+        const float r = rsqrtf(sum16(s0 + s1, mask) * (1.f / 128.f) + p.eps);
+        const uint64_t R = f2_pack(r, r);
         if constexpr (!BWD) {
-          float y[8];
+          uint64_t Y[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) y[i] = x[j][i] * (r * w[i]);
+          for (int q = 0; q < 4; ++q) Y[q] = f2_mul(X[q], f2_mul(R, W[q]));
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            res[i] = fmaf(y[i], c[i], -y[i + 4] * sn[i]);
-            res[i + 4] = fmaf(y[i + 4], c[i + 4], y[i] * sn[i + 4]);
+          for (int q = 0; q < 2; ++q) {
+            R4[q] = f2_fma(Y[q], C[q], f2_mul(Y[q + 2], NS[q]));
+            R4[q + 2] = f2_fma(Y[q + 2], C[q + 2], f2_mul(Y[q], S[q + 2]));
           }
         } else {
           // dy = dz * cos + rotate_half^T(dz * sin): the pair partner's dz * sin comes back with the opposite sign
-          float gx = 0.f, dy[8], xh[8];
+          uint64_t Gz[4], dY[4], XH[4];
+          unpack_pair2(gr[j], Gz);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            dy[i] = fmaf(g[j][i], c[i], g[j][i + 4] * sn[i + 4]);
-            dy[i + 4] = fmaf(g[j][i + 4], c[i + 4], -g[j][i] * sn[i]);
+          for (int q = 0; q < 2; ++q) {
+            dY[q] = f2_fma(Gz[q], C[q], f2_mul(Gz[q + 2], S[q + 2]));
+            dY[q + 2] = f2_fma(Gz[q + 2], C[q + 2], f2_mul(Gz[q], NS[q]));
           }
           const bool counted = h + j < nh;
+          uint64_t gacc = 0ull;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            xh[i] = x[j][i] * r;
-            dw[i] = fmaf(counted ? dy[i] : 0.f, xh[i], dw[i]);
-            dy[i] *= w[i];
-            gx = fmaf(dy[i], xh[i], gx);
+          for (int q = 0; q < 4; ++q) {
+            XH[q] = f2_mul(X[q], R);
+            if (counted) DW[q] = f2_fma(dY[q], XH[q], DW[q]);
+            dY[q] = f2_mul(dY[q], W[q]);
+            gacc = f2_fma(dY[q], XH[q], gacc);
           }
-          const float m = sum16(gx, mask) * (1.f / 128.f);
+          float g0, g1;
+          f2_unpack(gacc, g0, g1);
+          const float m = sum16(g0 + g1, mask) * (1.f / 128.f);
+          const uint64_t NM = f2_pack(-m, -m);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) res[i] = r * (dy[i] - xh[i] * m);
+          for (int q = 0; q < 4; ++q) R4[q] = f2_mul(f2_fma(XH[q], NM, dY[q]), R);
         }
-        if (h + j < nh) store_pair_bf16(op + (h + j) * o_h, res);
+        if (h + j < nh) {
+          float res[8];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) f2_unpack(R4[q], res[2 * q], res[2 * q + 1]);
+          store_pair_bf16(op + (h + j) * o_h, res);
+        }
       }
     }
   }
 
+  if constexpr (BWD) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) f2_unpack(DW[q], dw[2 * q], dw[2 * q + 1]);
+  }
   if constexpr (BWD) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

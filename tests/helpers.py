@@ -143,3 +143,52 @@ class ThreadRing:
         if errors:
             raise errors[0][1]
         return results
+
+
+class LazyPullRing(ThreadRing):
+    """Stand-in for the copy-engine exchange (``PeerRingComm``): nothing is snapshotted. The receiver PULLS from
+    the sender's live buffer, and here it does so at the latest moment the protocol allows (inside its ``wait``),
+    while the sender's ``wait`` blocks until that pull has happened. A schedule that overwrites a send buffer before
+    waiting for its exchange, or reads a receive buffer early, computes with wrong data under this model and fails
+    the comparison with the oracle. Send buffers must come from ``empty`` (the arena), as with the real thing."""
+
+    def __init__(self, cp_size: int):
+        super().__init__(cp_size)
+        self.read = [set() for _ in range(cp_size)]  # read[r]: sequence numbers of rank r's sends already pulled
+
+    def comm(self, rank: int):
+        ring = self
+        state = {"seq": 0, "arena": []}
+
+        class _Comm:
+            def begin(self, nbytes):
+                state["arena"] = []
+
+            def empty(self, numel, dtype):
+                t = torch.empty(numel, dtype=dtype)
+                state["arena"].append(t)
+                return t
+
+            def exchange(self, send, recv):
+                assert any(send.data_ptr() == t.data_ptr() for t in state["arena"]), "send buffer is not arena memory"
+                n = state["seq"]
+                state["seq"] += 1
+                with ring.cond:
+                    ring.mail[(rank + 1) % ring.cp_size][n] = send  # the live buffer, not a copy
+                    ring.cond.notify_all()
+                return recv, n
+
+            @staticmethod
+            def wait(handle):
+                recv, n = handle
+                prev = (rank - 1) % ring.cp_size
+                with ring.cond:
+                    if not ring.cond.wait_for(lambda: n in ring.mail[rank], timeout=120):
+                        raise TimeoutError(f"simulated rank {rank}: buffer {n} was never published")
+                    recv.copy_(ring.mail[rank].pop(n))  # pull now: whatever the sender's buffer holds at this time
+                    ring.read[prev].add(n)
+                    ring.cond.notify_all()
+                    if not ring.cond.wait_for(lambda: n in ring.read[rank], timeout=120):
+                        raise TimeoutError(f"simulated rank {rank}: buffer {n} was never read by its successor")
+
+        return _Comm()

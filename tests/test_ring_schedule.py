@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from helpers import OracleBlockBackend, ThreadRing
+from helpers import LazyPullRing, OracleBlockBackend, ThreadRing
 from oracle import attention_oracle as O
 from pithtrain_b200.operators.ring_attention import _ring
 from pithtrain_b200.operators.ring_attention import sharding as sh
@@ -48,6 +48,17 @@ def test_schedule_in_process(cp, layout):
     q, k, v, do = _problem(S, dtype=torch.float64)
     ring = ThreadRing(cp)
     res = ring.run(lambda r, comm: _rank_fwd_bwd(r, cp, comm, layout, q, k, v, do, 0.25, torch.float64))
+    _check_against_full(res, cp, layout, q, k, v, do, 0.25, 5e-6)
+
+
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+@pytest.mark.parametrize("cp", [2, 3, 8])
+def test_schedule_under_pull_exchange(cp, layout):
+    """The buffer discipline the copy-engine exchange needs: receivers read the sender's live buffer as late as the
+    protocol allows, so a buffer reused before its exchange was waited for would corrupt the result."""
+    S = 16 * cp * 2
+    q, k, v, do = _problem(S, dtype=torch.float64)
+    res = LazyPullRing(cp).run(lambda r, comm: _rank_fwd_bwd(r, cp, comm, layout, q, k, v, do, 0.25, torch.float64))
     _check_against_full(res, cp, layout, q, k, v, do, 0.25, 5e-6)
 
 
