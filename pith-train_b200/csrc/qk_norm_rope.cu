@@ -87,10 +87,10 @@ constexpr int kHeadChunk = 8;  // heads of one position that a half-warp walks t
 // cos/sin once and walks through the chunk's heads G rows at a time. The two half-warps of a warp shuffle under
 // their own masks, so one may run out of positions before the other.
 #ifndef PITH_QK_G_FWD
-#define PITH_QK_G_FWD 4
+#define PITH_QK_G_FWD 8
 #endif
 #ifndef PITH_QK_G_BWD
-#define PITH_QK_G_BWD 1
+#define PITH_QK_G_BWD 2
 #endif
 #ifndef PITH_QK_MINB_FWD
 #define PITH_QK_MINB_FWD 3
