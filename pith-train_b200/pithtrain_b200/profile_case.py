@@ -3,7 +3,7 @@
     python -m pithtrain_b200.profile_case [--shape qwen3|mla] [--seq 8192] [--repeat 2]
 
 Launch order per repeat: attn_fwd_kernel, delta_kernel, attn_bwd_kernel<kDkDv>, attn_bwd_kernel<kDq>,
-3 x cast_kernel, combine_kernel, and (head_dim 128) qk_norm_rope_kernel forward and backward. The working set (a few hundred MB) is larger than the 126 MB L2 and far below the
+3 x cast_kernel, combine_kernel, and qk_norm_rope_kernel (head_dim 128) or mla_assemble_kernel (MLA) forward and backward. The working set (a few hundred MB) is larger than the 126 MB L2 and far below the
 sizes at which a multi-pass profiler capture gets slow. Prints the CUDA-event time of each launch.
 """
 
@@ -42,6 +42,8 @@ def main() -> None:
     emb = torch.outer(torch.arange(S, dtype=torch.float32),
                       1.0 / (1e6 ** (torch.arange(0, dqk, 2, dtype=torch.float32) / dqk))).repeat(1, 2)[None]
     cos, sin = emb.cos().bfloat16().to(dev), emb.sin().bfloat16().to(dev)
+    kv_in = torch.randn(1, S, hq, 256, generator=g).bfloat16().to(dev)
+    kpe_in = torch.randn(1, S, 64, generator=g).bfloat16().to(dev)
 
     def timed(name, fn):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -62,6 +64,9 @@ def main() -> None:
         if dqk == 128:
             timed("qk_norm_rope_kernel fwd", lambda: K.qk_norm_rope_fwd(q, k, w_norm, w_norm, cos, sin, 1e-6))
             timed("qk_norm_rope_kernel bwd", lambda: K.qk_norm_rope_bwd(q, k, w_norm, w_norm, cos, sin, 1e-6, do, k))
+        else:
+            timed("mla_assemble_kernel fwd", lambda: K.mla_assemble_fwd(q, kv_in, kpe_in, cos[..., :64], sin[..., :64]))
+            timed("mla_assemble_kernel bwd", lambda: K.mla_assemble_bwd(cos[..., :64], sin[..., :64], q, k, v))
     K.check_device_status(dev)
 
 
