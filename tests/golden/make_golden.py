@@ -1,8 +1,8 @@
 """Generates the golden vectors under tests/golden/ by running the REFERENCE's own code on CPU.
 
-Run once in a container that has the PithTrain checkout (default /root/reference):
+Run once where a PithTrain checkout is available:
 
-    python tests/golden/make_golden.py [/path/to/PithTrain]
+    python tests/golden/make_golden.py /path/to/PithTrain      (or set PITHTRAIN_ROOT)
 
 What is executed from the reference (nothing is copied):
   * pithtrain.operators.ring_attention.standard._online_softmax_combine          (natural-log merge)
@@ -51,7 +51,10 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    import os
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PITHTRAIN_ROOT")
+    if not root:
+        raise SystemExit("usage: make_golden.py /path/to/PithTrain (or set PITHTRAIN_ROOT)")
     combine_nat, combine_log2, ref_attention = import_reference(root)
 
     # ---- combine: random partials, plus the sentinels the ring uses (-inf and finfo.min)
