@@ -34,7 +34,6 @@ attention arithmetic is pinned to the reference's test oracle, not to its GPU ou
 
 from __future__ import annotations
 
-import math
 
 import torch
 

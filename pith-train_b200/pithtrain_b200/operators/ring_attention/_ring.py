@@ -21,6 +21,8 @@ sm_100a kernels. Tests drive the same schedule over gloo with a backend of their
 
 from __future__ import annotations
 
+import os as _os
+
 import torch
 import torch.distributed as dist
 
@@ -192,8 +194,6 @@ def ring_backward(backend, comm: RingComm, q, k, v, out, lse, dout, scale: float
 # graphs enabled the complete forward (and backward) ring of one shape is captured once, NCCL exchanges included, and
 # replayed with a single launch. Opt-in, because a capture allocates static input/output buffers per shape and every
 # rank must take the same decision at the same call.
-import os as _os
-
 _graphs_enabled = _os.environ.get("PITH_B200_RING_CUDA_GRAPHS", "0") == "1"
 _graph_cache: dict = {}
 
