@@ -263,6 +263,24 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    # ---- the copy-engine exchange needs CUDA IPC between the ranks' processes; where the host forbids it, every rank
+    # fails alike while mapping its neighbour's memory, and all of them fall back to the NCCL exchange together
+    exchange_note = None
+    if use_peer:
+        ok = torch.ones(1, device=dev)
+        try:
+            step(q, k, v, do)
+            torch.cuda.synchronize()
+            kernels.check_device_status(dev)
+        except Exception as e:  # noqa: BLE001 - reported in the JSON line
+            ok.zero_()
+            exchange_note = f"copy-engine exchange unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL send/recv used"
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            use_peer = False
+            enable_peer_copies(False)
+            exchange_note = exchange_note or "copy-engine exchange unavailable on another rank; NCCL send/recv used"
+
     # ---- resident-input measurement (headline `value`)
     for _ in range(max(3, args.warmup)):
         step(q, k, v, do)
@@ -453,7 +471,8 @@ def main():
                     else f"{args.sharding} CP={world}" if world > 1 else "single GPU (CP=1)"),
                 "sharding": args.sharding if world > 1 else "none",
                 "ring_cuda_graphs": use_graphs,
-                "ring_exchange": "copy engines over peer-mapped memory" if use_peer else "NCCL send/recv",
+                "ring_exchange": exchange_note or ("copy engines over peer-mapped memory" if use_peer
+                                                   else "NCCL send/recv"),
                 "l2": "inputs + gradients per step exceed the 126 MB L2 (no flush needed)",
                 "flops_convention": "fwd B*H*S^2*(Dqk+Dv), bwd 2.5x fwd",
             },
