@@ -421,11 +421,8 @@ static int launch_fwd(const pith_attn_fwd_args* a, const FwdParams& p, cudaStrea
   if (int rc = make_tensor_map(&tk, a->k, 2, a->B, a->Sk, a->Hkv, a->Dqk, a->k_stride, 64, BN)) return rc;
   if (int rc = make_tensor_map(&tv, a->v, 2, a->B, a->Sk, a->Hkv, a->Dv, a->v_stride, 64, BN)) return rc;
   auto kern = attn_fwd_kernel<DQK, BN, KST, VST>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    PITH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
-    attr_set = true;
-  }
+  // per call: the attribute belongs to the current device, and a process may use several
+  PITH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc));
   dim3 grid((a->Sq + 2 * kBM - 1) / (2 * kBM), a->Hq, a->B);
   kern<<<grid, kFwdThreads, L::kAlloc, st>>>(tq, tk, tv, p);
   PITH_CUDA(cudaGetLastError());
