@@ -507,10 +507,13 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
     return mode == kDkDv ? launch_bwd<192, kDkDv>(a, p, s) : launch_bwd<192, kDq>(a, p, s);
   };
   // Side by side pays when a launch is only a few waves long (its partial last wave is a large share); on long
-  // launches the two kernels' interleaved CTAs cost more in L2 locality than the tail gives back
-  // (measured: 4096 x 4096 causal, 32 heads: 0.615 -> 0.563 ms; 8192 x 8192: 1.90 -> 2.01 ms).
+  // launches of the head_dim-128 kernels the two kernels' interleaved CTAs cost more in L2 locality than the tail
+  // gives back (measured, 32 heads: 4096 x 4096 causal 0.615 -> 0.563 ms, 6144 x 6144 causal 1.257 -> 1.152 ms,
+  // 8192 x 8192 causal 1.90 -> 2.01 ms). The Dqk = 192 kernels gain at every size measured (16 heads,
+  // 8192 x 8192 causal: 1.777 -> 1.636 ms).
   const double work = static_cast<double>(a->B) * a->Hq * a->Sq * a->Sk * (a->causal ? 0.5 : 1.0);
-  const bool side_by_side = (a->flags & PITH_BWD_CONCURRENT) || (!(a->flags & PITH_BWD_SERIAL) && work <= 5.4e8);
+  const double limit = a->Dqk == 128 ? 7.0e8 : 4.0e9;
+  const bool side_by_side = (a->flags & PITH_BWD_CONCURRENT) || (!(a->flags & PITH_BWD_SERIAL) && work <= limit);
   if (!(want_dkv && want_dq) || !side_by_side) {
     if (want_dkv)
       if (int rc = launch(kDkDv, st)) return rc;
