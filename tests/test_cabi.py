@@ -43,8 +43,9 @@ def test_struct_sizes_match_the_header(built_library):
         #include <stdio.h>
         #include "pith_b200.h"
         int main(void) {
-          printf("%zu %zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
-                 sizeof(pith_attn_bwd_args), sizeof(pith_combine_args), sizeof(pith_attn_bwd_noalloc_args));
+          printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
+                 sizeof(pith_attn_bwd_args), sizeof(pith_combine_args), sizeof(pith_attn_bwd_noalloc_args),
+                 sizeof(pith_qk_norm_rope_args), sizeof(pith_mla_assemble_args));
           return 0;
         }""")
     with tempfile.TemporaryDirectory() as d:
@@ -53,7 +54,8 @@ def test_struct_sizes_match_the_header(built_library):
         sizes = [int(x) for x in subprocess.run([str(Path(d) / "s")], capture_output=True, text=True, check=True).stdout.split()]
     assert sizes == [ctypes.sizeof(_lib.AttnFwdArgs), ctypes.sizeof(_lib.BwdPreprocessArgs),
                      ctypes.sizeof(_lib.AttnBwdArgs), ctypes.sizeof(_lib.CombineArgs),
-                     ctypes.sizeof(_lib.AttnBwdNoallocArgs)]
+                     ctypes.sizeof(_lib.AttnBwdNoallocArgs), ctypes.sizeof(_lib.QkNormRopeArgs),
+                     ctypes.sizeof(_lib.MlaAssembleArgs)]
 
 
 def test_host_side_rejections(built_library):
@@ -86,3 +88,28 @@ def test_host_side_rejections(built_library):
     assert b"no gradient accumulator" in lib.pith_last_error()
     with pytest.raises(_lib.PithLibraryError):
         _lib.check(-1, "demo")
+
+
+def test_host_side_rejections_of_the_front_end_and_peer_entries(built_library):
+    from pithtrain_b200 import _lib
+    lib = _lib.load()
+    r = _lib.QkNormRopeArgs()
+    r.B, r.S, r.Hq, r.Hkv, r.D = 1, 8, 2, 1, 64
+    assert lib.pith_qk_norm_rope_fwd(ctypes.byref(r), None) < 0
+    assert b"128 only" in lib.pith_last_error()
+    r.D, r.S = 128, 0
+    assert lib.pith_qk_norm_rope_fwd(ctypes.byref(r), None) == 0          # empty: nothing to do
+    r.S = 8
+    assert lib.pith_qk_norm_rope_bwd(ctypes.byref(r), None) < 0
+    assert b"null weight" in lib.pith_last_error()
+    m = _lib.MlaAssembleArgs()
+    m.B, m.S, m.H, m.Dnope, m.Drope, m.Dv = 1, 8, 2, 128, 32, 128
+    assert lib.pith_mla_assemble_fwd(ctypes.byref(m), None) < 0
+    assert b"supported" in lib.pith_last_error()
+    m.Drope, m.H = 64, 0
+    assert lib.pith_mla_assemble_bwd(ctypes.byref(m), None) == 0           # empty
+    assert lib.pith_flag_signal(None, None, None) < 0 and b"null flag" in lib.pith_last_error()
+    assert lib.pith_flag_wait(0x1000, 0x1000, 0.0, None, None) < 0 and b"max_seconds" in lib.pith_last_error()
+    assert lib.pith_ipc_open(None, None) < 0 and lib.pith_ipc_close(None) < 0
+    assert lib.pith_peer_copy(None, None, 0, None) == 0                    # nothing to copy
+    assert lib.pith_peer_copy(None, 0x1000, 16, None) < 0
