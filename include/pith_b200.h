@@ -44,6 +44,11 @@ extern "C" {
                                      Neither flag: the library decides by problem size (side by side for launches of
                                      a few waves, where the partial last wave matters). */
 
+#define PITH_BWD_DQ_STORE_BF16 4u /* `dq_acc` points at a bf16 [B][Sq][Hq][Dqk] OUTPUT (dq_stride in bf16 elements): the dQ
+                                     pass stores this block's complete, scaled dQ there instead of adding into an fp32
+                                     accumulator. For a backward that consists of this one block (CP = 1): no zero
+                                     fill, no final rounding pass. head_dim 128 only. */
+
 /* flags for pith_combine_args.flags */
 #define PITH_COMBINE_NATURAL 1u   /* LSEs are natural-log (standard.py) instead of log2 (mla.py) */
 

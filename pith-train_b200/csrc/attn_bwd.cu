@@ -489,7 +489,12 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
                "unsupported head dims Dqk=%d Dv=%d (supported: 128/128 and 192/128)", a->Dqk, a->Dv);
   PITH_REQUIRE(a->softmax_scale > 0.f, "softmax_scale must be positive");
   PITH_REQUIRE(a->Hq <= 65535 && a->B <= 65535, "Hq and B must fit a grid dimension");
-  PITH_REQUIRE((!want_dq || f32_rows_ok(a->dq_acc, a->dq_stride)) &&
+  const bool dq_bf16 = want_dq && (a->flags & PITH_BWD_DQ_STORE_BF16);
+  PITH_REQUIRE(!dq_bf16 || a->Dqk == 128, "PITH_BWD_DQ_STORE_BF16 is supported for head_dim 128 only");
+  PITH_REQUIRE(!dq_bf16 || (aligned16(a->dq_acc) && a->dq_stride[0] % 8 == 0 && a->dq_stride[1] % 8 == 0 &&
+                            a->dq_stride[2] % 8 == 0),
+               "the bf16 dQ output must be 16-byte aligned with 16-byte-multiple strides");
+  PITH_REQUIRE((!want_dq || dq_bf16 || f32_rows_ok(a->dq_acc, a->dq_stride)) &&
                    (!want_dkv || (f32_rows_ok(a->dk_acc, a->dk_stride) && f32_rows_ok(a->dv_acc, a->dv_stride))),
                "gradient accumulators must be 16-byte aligned with 16-byte-multiple strides");
   if (int rc = require_sm100()) return rc;
@@ -498,6 +503,7 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   p.dbg = a->debug; p.status = a->status;
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal ? 1 : 0; p.causal_off = a->causal_offset;
+  p.dq_store_bf16 = dq_bf16 ? 1 : 0;
   p.scale = a->softmax_scale; p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   for (int i = 0; i < 3; ++i) { p.dqs[i] = a->dq_stride[i]; p.dks[i] = a->dk_stride[i]; p.dvs[i] = a->dv_stride[i]; }
   for (int i = 0; i < 2; ++i) { p.ls[i] = a->lse_stride[i]; p.dls[i] = a->delta_stride[i]; }

@@ -497,8 +497,36 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (lane == 0 && (warp & 3) == 0) PROFM_WRITE(MODE * 32 + 16 + h * 4, 4);
 
-    // ---- write-out: accumulators -> scaled fp32 atomics
-    if (n_it > 0) {
+    // ---- write-out. dQ as a final result: one CTA owns the whole row block, so it is stored as bf16 directly
+    //      (zeros where the block sees no key); everything else: accumulators -> scaled fp32 atomics
+    if (MODE == kDq && p.dq_store_bf16) {
+      if (n_it > 0) {
+        mbar_wait(acc_full, 0, ctl, 0x900);
+        tc_fence_after_sync();
+      }
+      __nv_bfloat16* dstb = reinterpret_cast<__nv_bfloat16*>(p.dq_acc) + batch * p.dqs[0] +
+                            static_cast<int64_t>(res_row) * p.dqs[1] + head * p.dqs[2] + h * 64;
+      const uint32_t src = tmem_base + lane_addr + kColAcc + h * 64;
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t r[32];
+        if (n_it > 0) {
+          tmem_ld32(src + cc * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (res_row < p.Sq) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *(reinterpret_cast<uint4*>(dstb + cc * 32) + i) = make_uint4(
+                pack_bf16(__uint_as_float(r[8 * i]) * p.scale, __uint_as_float(r[8 * i + 1]) * p.scale),
+                pack_bf16(__uint_as_float(r[8 * i + 2]) * p.scale, __uint_as_float(r[8 * i + 3]) * p.scale),
+                pack_bf16(__uint_as_float(r[8 * i + 4]) * p.scale, __uint_as_float(r[8 * i + 5]) * p.scale),
+                pack_bf16(__uint_as_float(r[8 * i + 6]) * p.scale, __uint_as_float(r[8 * i + 7]) * p.scale));
+        }
+      }
+    } else if (n_it > 0) {
       mbar_wait(acc_full, 0, ctl, 0x900);
       tc_fence_after_sync();
       float* dst;

@@ -107,6 +107,7 @@ NOALLOC_SCRATCH_BYTES = 32 << 20
 FWD_O_FP32 = 1
 BWD_SERIAL = 1
 BWD_CONCURRENT = 2
+BWD_DQ_STORE_BF16 = 4
 FWD_LSE_NATURAL = 2
 COMBINE_NATURAL = 1
 DTYPE_BF16 = 0

@@ -120,11 +120,20 @@ def bwd_preprocess(o, dout, delta=None):
 
 
 def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool, causal_offset: int,
-             dq_acc, dk_acc, dv_acc, debug=None, serial=None):
+             dq_acc, dk_acc, dv_acc, debug=None, serial=None, dq_out=None):
     """Adds this block's dQ/dK/dV into the fp32 accumulators; see ``pith_attn_bwd``.
 
     ``serial=True`` runs the two passes one after the other on the current stream (``PITH_BWD_SERIAL``),
-    ``serial=False`` side by side (``PITH_BWD_CONCURRENT``); ``None`` lets the library decide by problem size."""
+    ``serial=False`` side by side (``PITH_BWD_CONCURRENT``); ``None`` lets the library decide by problem size.
+
+    ``dq_out`` (bf16, shape of q; head_dim 128 only; instead of ``dq_acc``): the dQ pass stores this block's complete
+    dQ there (``PITH_BWD_DQ_STORE_BF16``) — for a backward that consists of this one block."""
+    if dq_out is not None:
+        if dq_acc is not None:
+            raise ValueError("give dq_acc (accumulate, fp32) or dq_out (store, bf16), not both")
+        if dq_out.dtype != torch.bfloat16 or dq_out.shape != q.shape:
+            raise ValueError("dq_out must be bfloat16 with the shape of q")
+        _require_cuda(dq_out)
     _require_cuda(q, k, v, dout, lse_log2, delta, dq_acc, dk_acc, dv_acc)
     B, Sq, Hq, Dqk = q.shape
     _, Sk, Hkv, Dv = v.shape
@@ -134,22 +143,25 @@ def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool,
     a = _lib.AttnBwdArgs()
     a.q, a.k, a.v, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
     a.lse, a.delta = lse_log2.data_ptr(), delta.data_ptr()
-    a.dq_acc = dq_acc.data_ptr() if dq_acc is not None else None
+    a.dq_acc = dq_out.data_ptr() if dq_out is not None else dq_acc.data_ptr() if dq_acc is not None else None
     a.dk_acc = dk_acc.data_ptr() if dk_acc is not None else None
     a.dv_acc = dv_acc.data_ptr() if dv_acc is not None else None
     a.status = status_word(q.device).data_ptr()
     a.debug = debug.data_ptr() if debug is not None else None
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
-    a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), (0 if serial is None else _lib.BWD_SERIAL if serial else _lib.BWD_CONCURRENT)
+    a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), ((0 if serial is None else _lib.BWD_SERIAL if serial else _lib.BWD_CONCURRENT)
+                                                        | (_lib.BWD_DQ_STORE_BF16 if dq_out is not None else 0))
     a.softmax_scale = float(softmax_scale)
     a.q_stride, a.k_stride, a.v_stride, a.do_stride = _bshd(q, "q"), _bshd(k, "k"), _bshd(v, "v"), _bshd(dout, "dout")
-    if dq_acc is not None:
+    if dq_out is not None:
+        a.dq_stride = _bshd(dq_out, "dq_out")
+    elif dq_acc is not None:
         a.dq_stride = _bshd(dq_acc, "dq_acc")
     if dk_acc is not None:
         a.dk_stride, a.dv_stride = _bshd(dk_acc, "dk_acc"), _bshd(dv_acc, "dv_acc")
     a.lse_stride, a.delta_stride = _bhs(lse_log2, "lse"), _bhs(delta, "delta")
     _lib.check(_lib.load().pith_attn_bwd(ctypes.byref(a), _stream(q)), "pith_attn_bwd")
-    _count((dq_acc is not None) + (dk_acc is not None))
+    _count((dq_acc is not None or dq_out is not None) + (dk_acc is not None))
 
 
 def cast_to_bf16(acc, out=None, scale: float = 1.0):

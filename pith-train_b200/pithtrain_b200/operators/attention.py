@@ -39,9 +39,13 @@ def attn_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tens
     if do.stride(-1) != 1:
         do = do.contiguous()
     delta = K.bwd_preprocess(o, do)
-    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
     dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    if q.shape[-1] == 128:  # the dQ pass stores its bf16 result directly
+        dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        K.attn_bwd(q, k, v, do, lse, delta, softmax_scale, causal, 0, None, dk, dv, dq_out=dq)
+        return dq, K.cast_to_bf16(dk), K.cast_to_bf16(dv)
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     K.attn_bwd(q, k, v, do, lse, delta, softmax_scale, causal, 0, dq, dk, dv)
     return K.cast_to_bf16(dq), K.cast_to_bf16(dk), K.cast_to_bf16(dv)
 

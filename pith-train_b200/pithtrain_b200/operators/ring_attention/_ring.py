@@ -49,6 +49,17 @@ class CudaBlockBackend:
     def cast(self, acc):
         return self.k.cast_to_bf16(acc)
 
+    def bwd_single(self, q, k, v, do, lse, delta, scale, dk_acc, dv_acc):
+        """The whole backward is this one causal block (CP = 1): returns dQ. At head_dim 128 the dQ pass stores its
+        bf16 result directly (no zeroed fp32 accumulator, no rounding pass)."""
+        if q.shape[-1] == 128 and q.dtype == torch.bfloat16:
+            dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+            self.k.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, None, dk_acc, dv_acc, dq_out=dq)
+            return dq
+        dq_acc = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        self.k.attn_bwd(q, k, v, do, lse, delta, scale, True, 0, dq_acc, dk_acc, dv_acc)
+        return self.k.cast_to_bf16(dq_acc).to(q.dtype)
+
 
 class RingComm:
     """send-to-next / receive-from-previous over ``torch.distributed`` P2P, joined later.
@@ -143,13 +154,18 @@ def ring_backward(backend, comm: RingComm, q, k, v, out, lse, dout, scale: float
     sh.check_sharding(sharding)
     B, S, Hq, Dqk = q.shape
     delta = backend.delta(out, dout)
-    dq_acc = torch.zeros((B, S, Hq, Dqk), dtype=torch.float32, device=q.device)
     nk, nv = k.numel(), v.numel()
     if cp_size == 1:
         dkv = torch.zeros(nk + nv, dtype=torch.float32, device=q.device)
         dk_acc, dv_acc = _views(dkv, nk, k.shape, v.shape)
-        backend.bwd_block(q, k, v, dout, lse, delta, scale, True, dq_acc, dk_acc, dv_acc)
-        return backend.cast(dq_acc).to(q.dtype), backend.cast(dk_acc).to(k.dtype), backend.cast(dv_acc).to(v.dtype)
+        if hasattr(backend, "bwd_single"):
+            dq = backend.bwd_single(q, k, v, dout, lse, delta, scale, dk_acc, dv_acc)
+        else:
+            dq_acc = torch.zeros((B, S, Hq, Dqk), dtype=torch.float32, device=q.device)
+            backend.bwd_block(q, k, v, dout, lse, delta, scale, True, dq_acc, dk_acc, dv_acc)
+            dq = backend.cast(dq_acc).to(q.dtype)
+        return dq, backend.cast(dk_acc).to(k.dtype), backend.cast(dv_acc).to(v.dtype)
+    dq_acc = torch.zeros((B, S, Hq, Dqk), dtype=torch.float32, device=q.device)
     c = S // 2
     _begin(comm, (nk + nv) * (2 * k.element_size() + 3 * 4))
     bufs, _ = _pack_kv(comm, k, v)

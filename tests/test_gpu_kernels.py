@@ -509,3 +509,29 @@ def test_mla_assemble_full_size(K, cuda_device):
     with pytest.raises(ValueError):
         K.mla_assemble_fwd(q[..., :128], kv, k_pe, cos_t[pos], sin_t[pos])
     K.check_device_status(dev)
+
+
+@pytest.mark.parametrize("Sq,Sk,causal,off", [(512, 512, True, 0), (384, 640, False, 0), (200, 333, True, 133),
+                                              (512, 256, True, -300)])
+def test_backward_direct_dq_store(K, cuda_device, Sq, Sk, causal, off):
+    """PITH_BWD_DQ_STORE_BF16: the dQ pass stores bf16 directly. Must equal the rounded fp32 accumulator bit for bit
+    (one CTA owns a row block, so the sum is the same), including rows that see no key at all (zeros) and ragged
+    tile edges; and it must not touch dK/dV."""
+    dev = cuda_device
+    q, k, v, do = _inputs(1, Sq, Sk, 8, 2, 128, dev, seed=7)
+    scale = 128 ** -0.5
+    o, lse = K.attn_fwd(q, k, v, scale, causal, off)
+    lse = torch.nan_to_num(lse, nan=0.0, neginf=0.0)  # rows without keys: any finite value, their P is masked anyway
+    o = torch.nan_to_num(o)
+    delta = K.bwd_preprocess(o, do)
+    acc = [torch.zeros(t.shape, dtype=torch.float32, device=dev) for t in (q, k, v)]
+    K.attn_bwd(q, k, v, do, lse, delta, scale, causal, off, acc[0], acc[1], acc[2])
+    dq = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device=dev)
+    dk2, dv2 = (torch.zeros_like(t) for t in acc[1:])
+    K.attn_bwd(q, k, v, do, lse, delta, scale, causal, off, None, dk2, dv2, dq_out=dq)
+    assert torch.equal(dq, acc[0].bfloat16())
+    assert torch.allclose(dk2, acc[1], atol=1e-4, rtol=1e-4) and torch.allclose(dv2, acc[2], atol=1e-4, rtol=1e-4)
+    if off < 0:
+        assert not dq[:, : -off].any()  # queries before the first visible key
+    with pytest.raises(ValueError):
+        K.attn_bwd(q, k, v, do, lse, delta, scale, causal, off, acc[0], None, None, dq_out=dq)
