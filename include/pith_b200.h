@@ -31,11 +31,16 @@
 extern "C" {
 #endif
 
-#define PITH_B200_ABI_VERSION 1
+#define PITH_B200_ABI_VERSION 2
 
 /* flags for pith_attn_fwd_args.flags */
 #define PITH_FWD_O_FP32 1u        /* `o` is fp32 (running accumulator of a ring) instead of bf16 */
 #define PITH_FWD_LSE_NATURAL 2u   /* write natural-log LSE (flash-attn convention) instead of log2 */
+#define PITH_FWD_SINGLE_CTA 4u    /* use the kernel that runs every MMA inside one CTA */
+#define PITH_FWD_CTA_PAIR 8u      /* use the kernel in which pairs of CTAs (thread-block clusters of two) run every MMA
+                                     together and each stage half of every K/V block.
+                                     Neither flag: the library picks the faster one for the head dimensions (measured:
+                                     the pair kernel for Dqk = 192, the single-CTA kernel for Dqk = 128). */
 
 /* flags for pith_attn_bwd_args.flags */
 #define PITH_BWD_SERIAL 1u        /* run the dK/dV and dQ passes one after the other on `stream` */
@@ -64,7 +69,6 @@ typedef struct pith_attn_fwd_args {
   float* lse;             /* [B][Hq][Sq] */
   const float* prev_o;    /* optional fp32 [B][Sq][Hq][Dv]: partial result to merge in the epilogue */
   const float* prev_lse;  /* optional fp32 [B][Hq][Sq], log2 domain, paired with prev_o */
-  float* debug;           /* optional; internal bring-up dumps (3 * 128 * 128 + 256 floats) */
   uint32_t* status;       /* optional device status word */
   int32_t B, Sq, Sk, Hq, Hkv, Dqk, Dv;
   int32_t causal;         /* 0 = every key visible; 1 = key n visible to query m iff n <= m + causal_offset */
@@ -115,7 +119,6 @@ typedef struct pith_attn_bwd_args {
   float* dk_acc;      /* [B][Sk][Hkv][Dqk] fp32, accumulated into (+=); NULL (with dv_acc) = skip dK/dV */
   float* dv_acc;      /* [B][Sk][Hkv][Dv] fp32, accumulated into (+=) */
   uint32_t* status;
-  float* debug;
   int32_t B, Sq, Sk, Hq, Hkv, Dqk, Dv;
   int32_t causal, causal_offset;
   uint32_t flags;

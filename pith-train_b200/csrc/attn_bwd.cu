@@ -500,7 +500,7 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   if (int rc = require_sm100()) return rc;
   BwdParams p;
   p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk_acc = a->dk_acc; p.dv_acc = a->dv_acc;
-  p.dbg = a->debug; p.status = a->status;
+  p.status = a->status;
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal ? 1 : 0; p.causal_off = a->causal_offset;
   p.dq_store_bf16 = dq_bf16 ? 1 : 0;

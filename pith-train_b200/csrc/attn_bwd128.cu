@@ -28,19 +28,6 @@
 #include "common.cuh"
 #include "host_common.h"
 
-// Cycle accounting for bring-up (-DPITH_PROFILE): CTA 0 of head 0 adds up the cycles between markers per role and
-// writes them to the debug buffer. Compiled out otherwise.
-#ifdef PITH_PROFILE
-#define PROFM_DECL long long prof_t = clock64(), prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PROFM(i) do { const long long n__ = clock64(); prof_acc[i] += n__ - prof_t; prof_t = n__; } while (0)
-#define PROFM_WRITE(base, n) do { if (p.dbg != nullptr && blockIdx.x == 0 && head == 0 && batch == 0) { \
-    for (int i__ = 0; i__ < (n); ++i__) p.dbg[(base) + i__] = static_cast<float>(prof_acc[i__]); } } while (0)
-#else
-#define PROFM_DECL
-#define PROFM(i)
-#define PROFM_WRITE(base, n)
-#endif
-
 namespace pith {
 namespace bwd128 {
 
@@ -298,37 +285,29 @@ __global__ void __launch_bounds__(kThreads, 1)
       gemm_t2(x2k[0]);
       umma_commit(t2_full);
       if constexpr (MODE == kDq) umma_commit(&x2_empty[0]);  // V_0 is only read by dP(0)
-      PROFM_DECL;
       for (int k = 0; k < n_it; ++k) {
         const int s = k & 1, sn = s ^ 1;
         const bool more = k + 1 < n_it;
         if constexpr (MODE == kDkDv) {
           mbar_wait(p_full, k & 1, ctl, 0x400);
-          PROFM(0);
           tc_fence_after_sync();
           gemm_ts(tmem_base + kColAcc, t1, s ? x2m[1] : x2m[0], idesc_mn, k > 0);  // dV += P^T dO_i
           umma_commit(&x2_empty[s]);  // last use of dO_i
-          PROFM(1);
           if (more) {
             mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
-            PROFM(2);
             tc_fence_after_sync();
             gemm_t1(sn ? x1k[1] : x1k[0]);  // S^T(k+1)
             umma_commit(t1_full);
-            PROFM(3);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
-          PROFM(4);
           tc_fence_after_sync();
           gemm_ts(tmem_base + kColAcc2, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0);  // dK += dS^T Q_i
           umma_commit(&x_empty[s]);
-          PROFM(5);
           if (more) {
             mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
             tc_fence_after_sync();
             gemm_t2(sn ? x2k[1] : x2k[0]);  // dP^T(k+1)
             umma_commit(t2_full);
-            PROFM(6);
           }
         } else {
           if (more) {
@@ -351,8 +330,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      PROFM_WRITE(MODE * 32, 7);
-      if (p.dbg != nullptr && blockIdx.x == 0 && head == 0 && batch == 0) p.dbg[MODE * 32 + 7] = static_cast<float>(n_it);
       umma_commit(acc_full);
     }
   } else if (warp >= 4) {
@@ -383,7 +360,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_arrive(rt_full);
       }
     }
-    PROFM_DECL;
     for (int k = 0; k < n_it; ++k) {
       const int s = k & 1;
       const int x0 = (it_begin + k) * kT + h * 64;  // global position of this thread's first column
@@ -400,21 +376,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         need_mask = p.causal && (x0 + 63 > r0 + p.causal_off);
         lim = res_row + p.causal_off - x0;
       }
-#ifdef PITH_SKIP_MATH  // experiment: tensor-core + TMA pipeline alone (results are garbage)
-      mbar_wait(t1_full, k & 1, ctl, 0x700);
-      PROFM(0);
-      tc_fence_before_sync();
-      mbar_arrive(p_full);
-      mbar_wait(t2_full, k & 1, ctl, 0x800);
-      PROFM(2);
-      tc_fence_before_sync();
-      mbar_arrive(ds_full);
-      (void)need_mask; (void)lim; (void)st_l; (void)st_d; (void)c2; (void)my_nl2; (void)my_nd2;
-      continue;
-#endif
       // ---- P = exp2(S c - lse)
       mbar_wait(t1_full, k & 1, ctl, 0x700);
-      PROFM(0);
       tc_fence_after_sync();
       uint32_t pv[64];  // scores, then probabilities (fp32 bit patterns)
       tmem_ld32(t1, pv);
@@ -461,10 +424,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_before_sync();
         mbar_arrive(p_full);
       }
-      PROFM(1);
       // ---- dS = P (dP - delta)
       mbar_wait(t2_full, k & 1, ctl, 0x800);
-      PROFM(2);
       tc_fence_after_sync();
       uint32_t dp[64];
       tmem_ld32(t2, dp);
@@ -493,9 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(ds_full);
-      PROFM(3);
     }
-    if (lane == 0 && (warp & 3) == 0) PROFM_WRITE(MODE * 32 + 16 + h * 4, 4);
 
     // ---- write-out. dQ as a final result: one CTA owns the whole row block, so it is stored as bf16 directly
     //      (zeros where the block sees no key); everything else: accumulators -> scaled fp32 atomics

@@ -15,7 +15,6 @@ struct BwdParams {
   float* dq_acc;
   float* dk_acc;
   float* dv_acc;
-  float* dbg;
   uint32_t* status;
   int B, Sq, Sk, Hq, Hkv;
   int causal, causal_off;

@@ -17,38 +17,9 @@
 // 2^8 (warp-uniform decision), which keeps the O rescale off the common path. The epilogue
 // normalises, optionally merges a previous partial (O, LSE) (the ring's online-softmax combine)
 // and writes bf16 or fp32 O plus the log2-domain LSE.
-#include "../../include/pith_b200.h"
-#include "common.cuh"
-#include "host_common.h"
-
-#ifndef PITH_FWD_REGS_LO
-#define PITH_FWD_REGS_LO 64
-#define PITH_FWD_REGS_HI 216
-#endif
-#ifndef PITH_PACKED_F32
-#define PITH_PACKED_F32 1  // scale / sum the scores with fma.f32x2 / add.f32x2 (two floats per instruction)
-#endif
+#include "attn_fwd_common.cuh"
 
 namespace pith {
-
-struct FwdParams {
-  void* o;
-  float* lse;
-  const float* prev_o;
-  const float* prev_lse;
-  float* dbg;
-  uint32_t* status;
-  int B, Sq, Sk, Hq, Hkv;
-  int causal, causal_off;
-  int o_fp32, lse_natural;
-  float scale_log2;
-  int64_t os[3], pos[3];
-  int64_t ls[2], pls[2];
-};
-
-constexpr int kFwdThreads = 384;
-constexpr int kBM = 128;  // query rows per tile
-constexpr int kDV = 128;
 
 template <int DQK, int BN, int KST, int VST>
 struct FwdSmem {
@@ -155,7 +126,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   // (each role branch below starts with its own setmaxnreg so that the limit holds for exactly that code)
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    setmaxnreg_dec<PITH_FWD_REGS_LO>();
+    setmaxnreg_dec<kFwdRegsLo>();
     if (lane == 0 && nmax > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
@@ -182,7 +153,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    setmaxnreg_dec<PITH_FWD_REGS_LO>();
+    setmaxnreg_dec<kFwdRegsLo>();
     if (lane == 0 && nmax > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(kBM, BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, kDV, false, true);
@@ -230,172 +201,18 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ softmax + epilogue
-    setmaxnreg_inc<PITH_FWD_REGS_HI>();
+    setmaxnreg_inc<kFwdRegsHi>();
     const int t = (warp - 4) >> 2;                 // query tile of this warpgroup
     const int row_in_tile = ((warp & 3) << 5) + lane;  // TMEM lane == query row
     const int row = m0 + t * kBM + row_in_tile;    // query position inside this call's Q block
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) << 5) << 16;
     const uint32_t tS = tmem_base + lane_addr + t * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
-    const float c = p.scale_log2;
-    const int nb = nblk[t];
-
-    float m_used = -INFINITY;
-    float l = 0.f;
-    for (int j = 0; j < nb; ++j) {
-      mbar_wait(&s_full[t], j & 1, ctl, 0x700 + t);
-      tc_fence_after_sync();
-      uint32_t sr[BN];
-#pragma unroll
-      for (int cchunk = 0; cchunk < BN / 32; ++cchunk) tmem_ld32(tS + cchunk * 32, sr + cchunk * 32);
-      tmem_wait_ld();
-      const int n0 = j * BN;
-      const bool need_mask = (p.causal && (n0 + BN - 1 > m0 + t * kBM + p.causal_off)) || (n0 + BN > p.Sk);
-      if (need_mask) {
-        const int limit = p.causal ? min(p.Sk - 1, row + p.causal_off) : p.Sk - 1;  // last visible key
-#pragma unroll
-        for (int i = 0; i < BN; ++i)
-          if (n0 + i > limit) sr[i] = 0xFF800000u;  // -inf
-      }
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
-#pragma unroll
-      for (int i = 0; i < BN; i += 8) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          mx[u] = fmax3(mx[u], __uint_as_float(sr[i + 2 * u]), __uint_as_float(sr[i + 2 * u + 1]));
-      }
-      const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_used, m_blk);
-      if (j == 0) {
-        m_used = m_new;
-      } else {
-        const bool need = (m_new - m_used) * c > 8.0f;
-        if (__any_sync(0xFFFFFFFFu, need)) {
-          const float alpha = need ? fast_exp2((m_used - m_new) * c) : 1.0f;
-          if (need) m_used = m_new;
-          l *= alpha;
-#pragma unroll
-          for (int cchunk = 0; cchunk < kDV / 32; ++cchunk) {
-            uint32_t orr[32];
-            tmem_ld32(tO + cchunk * 32, orr);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-            tmem_st32(tO + cchunk * 32, orr);
-          }
-        }
-      }
-      const float mc = (m_used == -INFINITY) ? 0.f : m_used * c;
-#if PITH_PACKED_F32
-      const uint64_t c2 = f2_pack(c, c), nmc2 = f2_pack(-mc, -mc);
-      uint64_t ls2[2] = {0ull, 0ull};  // four independent partial sums, packed in pairs
-#pragma unroll
-      for (int cchunk = 0; cchunk < BN / 64; ++cchunk) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const uint64_t x2 = f2_fma(f2_pack(__uint_as_float(sr[cchunk * 64 + 2 * i]),
-                                             __uint_as_float(sr[cchunk * 64 + 2 * i + 1])), c2, nmc2);
-          float x0, x1;
-          f2_unpack(x2, x0, x1);
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-          ls2[i & 1] = f2_add(ls2[i & 1], f2_pack(p0, p1));
-          pk[i] = pack_bf16(p0, p1);
-        }
-        tmem_st32(tS + cchunk * 32, pk);
-      }
-      float la, lb, lc, ld;
-      f2_unpack(ls2[0], la, lb);
-      f2_unpack(ls2[1], lc, ld);
-      const float lsum = (la + lb) + (lc + ld);
-#else
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};  // independent partial sums
-#pragma unroll
-      for (int cchunk = 0; cchunk < BN / 64; ++cchunk) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cchunk * 64 + 2 * i]), c, -mc));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cchunk * 64 + 2 * i + 1]), c, -mc));
-          ls[(2 * i) & 3] += p0;
-          ls[(2 * i + 1) & 3] += p1;
-          pk[i] = pack_bf16(p0, p1);
-        }
-        tmem_st32(tS + cchunk * 32, pk);
-      }
-      const float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
-#endif
-      l += lsum;
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(&p_full[t]);
-    }
-
-    // ---- epilogue: normalise, optional merge with a previous partial, store
-    if (nb > 0) {
-      mbar_wait(&o_full[t], 0, ctl, 0x800 + t);
-      tc_fence_after_sync();
-    }
-    const bool row_ok = row < p.Sq;
-    float inv = (l > 0.f) ? 1.0f / l : 0.f;
-    float lse2 = (l > 0.f) ? fmaf(m_used, c, fast_log2(l)) : -INFINITY;
-    float w_prev = 0.f;
-    if (p.prev_o != nullptr) {
-      const float pl = row_ok ? p.prev_lse[batch * p.pls[0] + head * p.pls[1] + row] : -INFINITY;
-      const float mx = fmaxf(pl, lse2);
-      if (mx > -INFINITY) {
-        const float e1 = exp2f(pl - mx), e2 = exp2f(lse2 - mx);
-        const float den = e1 + e2;
-        w_prev = e1 / den;
-        inv *= e2 / den;
-        lse2 = mx + log2f(den);
-      }
-    }
-    if (row_ok) p.lse[batch * p.ls[0] + head * p.ls[1] + row] = p.lse_natural ? lse2 * 0.6931471805599453f : lse2;
-    const int64_t o_off = batch * p.os[0] + static_cast<int64_t>(row) * p.os[1] + head * p.os[2];
-    const int64_t po_off = batch * p.pos[0] + static_cast<int64_t>(row) * p.pos[1] + head * p.pos[2];
-#pragma unroll
-    for (int cchunk = 0; cchunk < kDV / 32; ++cchunk) {
-      uint32_t orr[32];
-      if (nb > 0) {
-        tmem_ld32(tO + cchunk * 32, orr);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) orr[i] = 0u;
-      }
-      if (row_ok) {
-        float ov[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) ov[i] = __uint_as_float(orr[i]) * inv;
-        if (p.prev_o != nullptr) {
-          const float4* pp = reinterpret_cast<const float4*>(p.prev_o + po_off + cchunk * 32);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 x = pp[i];
-            ov[4 * i] = fmaf(w_prev, x.x, ov[4 * i]);
-            ov[4 * i + 1] = fmaf(w_prev, x.y, ov[4 * i + 1]);
-            ov[4 * i + 2] = fmaf(w_prev, x.z, ov[4 * i + 2]);
-            ov[4 * i + 3] = fmaf(w_prev, x.w, ov[4 * i + 3]);
-          }
-        }
-        if (p.o_fp32) {
-          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + o_off + cchunk * 32);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) dst[i] = make_float4(ov[4 * i], ov[4 * i + 1], ov[4 * i + 2], ov[4 * i + 3]);
-        } else {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.o) + o_off + cchunk * 32);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[i] = make_uint4(pack_bf16(ov[8 * i], ov[8 * i + 1]), pack_bf16(ov[8 * i + 2], ov[8 * i + 3]),
-                                pack_bf16(ov[8 * i + 4], ov[8 * i + 5]), pack_bf16(ov[8 * i + 6], ov[8 * i + 7]));
-        }
-      }
-    }
-  }
-
-  else {
-    setmaxnreg_dec<PITH_FWD_REGS_LO>();  // warps 2 and 3 only give their registers away
+    uint64_t* pf = &p_full[t];
+    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf] { mbar_arrive(pf); }, tS, tO, m0 + t * kBM, row, nblk[t],
+                         head, batch, t);
+  } else {
+    setmaxnreg_dec<kFwdRegsLo>();  // warps 2 and 3 only give their registers away
   }
 
   // ------------------------------------------------------------------ teardown
@@ -455,7 +272,7 @@ extern "C" int pith_attn_fwd(const pith_attn_fwd_args* a, void* stream) {
                  "prev_o must be 16-byte aligned with 16-byte-multiple strides");
   if (int rc = require_sm100()) return rc;
   FwdParams p;
-  p.o = a->o; p.lse = a->lse; p.prev_o = a->prev_o; p.prev_lse = a->prev_lse; p.dbg = a->debug; p.status = a->status;
+  p.o = a->o; p.lse = a->lse; p.prev_o = a->prev_o; p.prev_lse = a->prev_lse; p.status = a->status;
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal ? 1 : 0; p.causal_off = a->causal_offset;
   p.o_fp32 = o32 ? 1 : 0; p.lse_natural = (a->flags & PITH_FWD_LSE_NATURAL) ? 1 : 0;
@@ -463,6 +280,10 @@ extern "C" int pith_attn_fwd(const pith_attn_fwd_args* a, void* stream) {
   for (int i = 0; i < 3; ++i) { p.os[i] = a->o_stride[i]; p.pos[i] = a->prev_o ? a->prev_o_stride[i] : 0; }
   for (int i = 0; i < 2; ++i) { p.ls[i] = a->lse_stride[i]; p.pls[i] = a->prev_lse ? a->prev_lse_stride[i] : 0; }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  PITH_REQUIRE(!((a->flags & PITH_FWD_SINGLE_CTA) && (a->flags & PITH_FWD_CTA_PAIR)),
+               "PITH_FWD_SINGLE_CTA and PITH_FWD_CTA_PAIR exclude each other");
+  const bool pair = (a->flags & PITH_FWD_CTA_PAIR) || (!(a->flags & PITH_FWD_SINGLE_CTA) && a->Dqk == 192);
+  if (pair) return launch_fwd_pair(a, p, st);
   if (a->Dqk == 128) return launch_fwd<128, 128, 2, 2>(a, p, st);
   return launch_fwd<192, 128, 2, 1>(a, p, st);
 }

@@ -21,7 +21,7 @@ I64x2 = c_int64 * 2
 class AttnFwdArgs(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("lse", c_void_p),
-        ("prev_o", c_void_p), ("prev_lse", c_void_p), ("debug", c_void_p), ("status", c_void_p),
+        ("prev_o", c_void_p), ("prev_lse", c_void_p), ("status", c_void_p),
         ("B", c_int32), ("Sq", c_int32), ("Sk", c_int32), ("Hq", c_int32), ("Hkv", c_int32),
         ("Dqk", c_int32), ("Dv", c_int32),
         ("causal", c_int32), ("causal_offset", c_int32), ("flags", c_uint32), ("softmax_scale", c_float),
@@ -43,7 +43,7 @@ class AttnBwdArgs(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("dout", c_void_p), ("lse", c_void_p),
         ("delta", c_void_p), ("dq_acc", c_void_p), ("dk_acc", c_void_p), ("dv_acc", c_void_p),
-        ("status", c_void_p), ("debug", c_void_p),
+        ("status", c_void_p),
         ("B", c_int32), ("Sq", c_int32), ("Sk", c_int32), ("Hq", c_int32), ("Hkv", c_int32),
         ("Dqk", c_int32), ("Dv", c_int32),
         ("causal", c_int32), ("causal_offset", c_int32), ("flags", c_uint32), ("softmax_scale", c_float),
@@ -109,6 +109,8 @@ BWD_SERIAL = 1
 BWD_CONCURRENT = 2
 BWD_DQ_STORE_BF16 = 4
 FWD_LSE_NATURAL = 2
+FWD_SINGLE_CTA = 4
+FWD_CTA_PAIR = 8
 COMBINE_NATURAL = 1
 DTYPE_BF16 = 0
 DTYPE_F32 = 1

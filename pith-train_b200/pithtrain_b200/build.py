@@ -20,7 +20,7 @@ INCLUDE_DIR = PKG_DIR.parent.parent / "include"
 BUILD_DIR = CSRC_DIR / "build"
 LIB_PATH = Path(os.environ.get("PITH_B200_LIB", PKG_DIR / "libpith_b200.so"))
 
-SOURCES = ["host_common.cu", "elementwise.cu", "attn_fwd.cu", "attn_bwd.cu", "attn_bwd128.cu", "noalloc.cu", "peer.cu",
+SOURCES = ["host_common.cu", "elementwise.cu", "attn_fwd.cu", "attn_fwd_pair.cu", "attn_bwd.cu", "attn_bwd128.cu", "noalloc.cu", "peer.cu",
            "qk_norm_rope.cu", "mla_assemble.cu"]
 
 NVCC_FLAGS = [

@@ -68,8 +68,11 @@ def _require_cuda(*ts):
 
 
 def attn_fwd(q, k, v, softmax_scale: float, causal: bool, causal_offset: int = 0, *, out=None, lse=None,
-             prev_o=None, prev_lse=None, out_fp32: bool = False, lse_natural: bool = False, debug=None):
-    """One attention block: returns (O [B,Sq,Hq,Dv], LSE [B,Hq,Sq]); see ``pith_attn_fwd``."""
+             prev_o=None, prev_lse=None, out_fp32: bool = False, lse_natural: bool = False, single_cta=None):
+    """One attention block: returns (O [B,Sq,Hq,Dv], LSE [B,Hq,Sq]); see ``pith_attn_fwd``.
+
+    ``single_cta=True`` selects the kernel that keeps every MMA inside one CTA (``PITH_FWD_SINGLE_CTA``),
+    ``single_cta=False`` the CTA-pair kernel (``PITH_FWD_CTA_PAIR``); ``None`` lets the library choose."""
     _require_cuda(q, k, v, out, lse, prev_o, prev_lse)
     B, Sq, Hq, Dqk = q.shape
     _, Sk, Hkv, Dv = v.shape
@@ -85,11 +88,11 @@ def attn_fwd(q, k, v, softmax_scale: float, causal: bool, causal_offset: int = 0
     a.q, a.k, a.v, a.o, a.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
     a.prev_o = prev_o.data_ptr() if prev_o is not None else None
     a.prev_lse = prev_lse.data_ptr() if prev_lse is not None else None
-    a.debug = debug.data_ptr() if debug is not None else None
     a.status = status_word(q.device).data_ptr()
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
     a.causal, a.causal_offset = int(bool(causal)), int(causal_offset)
-    a.flags = (_lib.FWD_O_FP32 if out_fp32 else 0) | (_lib.FWD_LSE_NATURAL if lse_natural else 0)
+    a.flags = ((_lib.FWD_O_FP32 if out_fp32 else 0) | (_lib.FWD_LSE_NATURAL if lse_natural else 0)
+               | (0 if single_cta is None else _lib.FWD_SINGLE_CTA if single_cta else _lib.FWD_CTA_PAIR))
     a.softmax_scale = float(softmax_scale)
     a.q_stride, a.k_stride, a.v_stride = _bshd(q, "q"), _bshd(k, "k"), _bshd(v, "v")
     a.o_stride = _bshd(out, "out")
@@ -120,7 +123,7 @@ def bwd_preprocess(o, dout, delta=None):
 
 
 def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool, causal_offset: int,
-             dq_acc, dk_acc, dv_acc, debug=None, serial=None, dq_out=None):
+             dq_acc, dk_acc, dv_acc, serial=None, dq_out=None):
     """Adds this block's dQ/dK/dV into the fp32 accumulators; see ``pith_attn_bwd``.
 
     ``serial=True`` runs the two passes one after the other on the current stream (``PITH_BWD_SERIAL``),
@@ -147,7 +150,6 @@ def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool,
     a.dk_acc = dk_acc.data_ptr() if dk_acc is not None else None
     a.dv_acc = dv_acc.data_ptr() if dv_acc is not None else None
     a.status = status_word(q.device).data_ptr()
-    a.debug = debug.data_ptr() if debug is not None else None
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk, a.Dv = B, Sq, Sk, Hq, Hkv, Dqk, Dv
     a.causal, a.causal_offset, a.flags = int(bool(causal)), int(causal_offset), ((0 if serial is None else _lib.BWD_SERIAL if serial else _lib.BWD_CONCURRENT)
                                                         | (_lib.BWD_DQ_STORE_BF16 if dq_out is not None else 0))

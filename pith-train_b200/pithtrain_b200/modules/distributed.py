@@ -13,8 +13,9 @@ from __future__ import annotations
 
 import atexit
 import os
+from contextlib import contextmanager
 from dataclasses import dataclass
-from typing import Optional
+from typing import Generator, Optional
 
 import torch
 import torch.distributed as dist
@@ -87,6 +88,21 @@ def setup_device_mesh(cfg: DistributedCfg, ctx: DistributedCtx) -> None:
     ctx.pp_rank = ctx.device_mesh.get_local_rank("pp")
     ctx.cp_rank = ctx.device_mesh.get_local_rank("cp")
     ctx.ep_rank = ctx.device_mesh.get_local_rank("ep")
+
+
+@contextmanager
+def distributed_context(cfg: object, ctx: object) -> Generator[DistributedCtx, None, None]:
+    """Brings the distributed runtime up for a task (reference: distributed.py:182-194): ``cfg.distributed`` and
+    ``ctx.distributed`` hold the configuration and the context; the default group and the device mesh exist inside
+    the ``with`` body. The matmul precision switches are the reference's and only matter where CUDA is present."""
+    assert hasattr(cfg, "distributed") and isinstance(cfg.distributed, DistributedCfg)
+    assert hasattr(ctx, "distributed") and isinstance(ctx.distributed, DistributedCtx)
+    if torch.cuda.is_available():
+        torch.backends.cuda.matmul.allow_tf32 = True
+        torch.set_float32_matmul_precision("high")
+    setup_default_process_group(cfg.distributed, ctx.distributed)
+    setup_device_mesh(cfg.distributed, ctx.distributed)
+    yield ctx.distributed
 
 
 def get_cp_group(ctx: DistributedCtx):

@@ -30,7 +30,7 @@ def test_header_symbols_are_all_exported(built_library):
 def test_abi_version_and_status_strings(built_library):
     from pithtrain_b200 import _lib
     lib = _lib.load()
-    assert lib.pith_abi_version() == 1
+    assert lib.pith_abi_version() == 2
     assert lib.pith_status_string(0) == b"ok"
     assert b"timed out" in lib.pith_status_string((1 << 24) | 0x700)
 

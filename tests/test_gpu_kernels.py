@@ -47,11 +47,12 @@ FWD_CASES = [
 ]
 
 
+@pytest.mark.parametrize("single_cta", [False, True], ids=["cta_pair", "single_cta"])
 @pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,Dqk,causal,off", FWD_CASES)
-def test_forward_matches_oracle(K, cuda_device, B, Sq, Sk, Hq, Hkv, Dqk, causal, off):
+def test_forward_matches_oracle(K, cuda_device, B, Sq, Sk, Hq, Hkv, Dqk, causal, off, single_cta):
     q, k, v, _ = _inputs(B, Sq, Sk, Hq, Hkv, Dqk, cuda_device)
     scale = Dqk ** -0.5
-    out, lse = K.attn_fwd(q, k, v, scale, causal, off)
+    out, lse = K.attn_fwd(q, k, v, scale, causal, off, single_cta=single_cta)
     ro, rl = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, causal, off)
     assert out.dtype == torch.bfloat16 and lse.dtype == torch.float32
     assert_bf16_close(out, ro, "O")
