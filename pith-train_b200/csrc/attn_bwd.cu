@@ -35,7 +35,7 @@ namespace pith {
 
 constexpr int kBwdThreads = 384;
 constexpr int kBwdRegsLo = 72;   // producer / MMA-issuer warpgroup
-constexpr int kBwdRegsHi = 208;  // compute warpgroups (128 * 72 + 256 * 208 <= 65536)
+constexpr int kBwdRegsHi = 208;  // compute warpgroups (128 * 72 + 256 * 208 <= 384 * 168, the launch allocation)
 constexpr int kRes = 128;  // rows of the resident tile (= TMEM lanes)
 constexpr int kStr = 64;   // rows of a streamed tile (= columns of T1 / T2)
 
@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     setmaxnreg_dec<kBwdRegsLo>();
-    if (lane == 0 && n_it > 0) {
+    const bool leader = elect_one();  // the whole warp walks the loop; one lane issues
+    if (n_it > 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(kRes, kStr, false, false);
       constexpr uint32_t idesc_dv = make_idesc_bf16(kRes, 128, false, true);
       constexpr uint32_t idesc_dqk = make_idesc_bf16(kRes, DQK, false, true);
@@ -208,16 +209,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll
         for (int kk = 0; kk < DQK / 16; ++kk) {
           const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-          umma_ss(t1, desc_advance(r1d, sub * (kRes * 128) + off), desc_advance(x1s, sub * (kStr * 128) + off), idesc_t,
-                  kk > 0 ? 1u : 0u);
+          if (leader)
+            umma_ss(t1, desc_advance(r1d, sub * (kRes * 128) + off), desc_advance(x1s, sub * (kStr * 128) + off), idesc_t,
+                    kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-          umma_ss(t2, desc_advance(r2d, sub * (kRes * 128) + off), desc_advance(x2s, sub * (kStr * 128) + off), idesc_t,
-                  kk > 0 ? 1u : 0u);
+          if (leader)
+            umma_ss(t2, desc_advance(r2d, sub * (kRes * 128) + off), desc_advance(x2s, sub * (kStr * 128) + off), idesc_t,
+                    kk > 0 ? 1u : 0u);
         }
-        umma_commit(&t_full[k & 1]);
+        if (leader) umma_commit(&t_full[k & 1]);
       };
       issue_t(0);
       for (int k = 0; k < n_it; ++k) {
@@ -231,20 +234,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         if constexpr (MODE == kDkDv) {
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dV += P^T dO_i
-            umma_ts(tmem_base + C::kAccCol, a1 + kk * 8, desc_advance(x2s, kk * 2048), idesc_dv, acc | (kk > 0 ? 1u : 0u));
+            if (leader)
+              umma_ts(tmem_base + C::kAccCol, a1 + kk * 8, desc_advance(x2s, kk * 2048), idesc_dv, acc | (kk > 0 ? 1u : 0u));
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dK += dS^T Q_i
-            umma_ts(tmem_base + C::kAccCol + 128, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk,
-                    acc | (kk > 0 ? 1u : 0u));
+            if (leader)
+              umma_ts(tmem_base + C::kAccCol + 128, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk,
+                      acc | (kk > 0 ? 1u : 0u));
         } else {
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dQ += dS K_j
-            umma_ts(tmem_base + C::kAccCol, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
+            if (leader)
+              umma_ts(tmem_base + C::kAccCol, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
         }
-        umma_commit(&x_empty[s]);
+        if (leader) umma_commit(&x_empty[s]);
         if (NBUF == 1 && k + 1 < n_it) issue_t(k + 1);
       }
-      umma_commit(acc_full);
+      if (leader) umma_commit(acc_full);
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ compute groups

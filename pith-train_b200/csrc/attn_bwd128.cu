@@ -58,28 +58,29 @@ constexpr uint32_t kColT1 = 0, kColT2 = 128, kColAcc = 256, kColAcc2 = 384;
 constexpr uint32_t kColR1 = 384, kColR2 = 448;
 
 // D[128 x 128] = A[128 x 128] * B[128 x 128]^T, both K-major in shared memory (two [128][64] sub-tiles each).
-__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool leader) {
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
     const uint32_t off = (kk >> 2) * (kT * 128) + (kk & 3) * 32;
-    umma_ss(d_tmem, desc_advance(adesc, off), desc_advance(bdesc, off), idesc, kk > 0 ? 1u : 0u);
+    if (leader) umma_ss(d_tmem, desc_advance(adesc, off), desc_advance(bdesc, off), idesc, kk > 0 ? 1u : 0u);
   }
 }
 // D[128 x 128] (+)= A[128 x 128] (packed bf16 in TMEM, halves at columns +0 and +64) * B (MN-major tile in shared memory)
-__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc) {
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc,
+                                        bool leader) {
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
     const uint32_t a = a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-    umma_ts(d_tmem, a, desc_advance(bdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
+    if (leader) umma_ts(d_tmem, a, desc_advance(bdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
   }
 }
 
 // D[128 x 128] = A[128 x 128] (packed bf16 in TMEM, 64 consecutive columns) * B[128 x 128]^T (K-major in shared memory)
-__device__ __forceinline__ void gemm_tk(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc) {
+__device__ __forceinline__ void gemm_tk(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool leader) {
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
     const uint32_t off = (kk >> 2) * (kT * 128) + (kk & 3) * 32;
-    umma_ts(d_tmem, a_tmem + kk * 8, desc_advance(bdesc, off), idesc, kk > 0 ? 1u : 0u);
+    if (leader) umma_ts(d_tmem, a_tmem + kk * 8, desc_advance(bdesc, off), idesc, kk > 0 ? 1u : 0u);
   }
 }
 // Row `row` of a [128][128] bf16 tile (two swizzled [128][64] sub-tiles in shared memory) -> 64 packed TMEM columns.
@@ -251,7 +252,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     setmaxnreg_dec<kRegsLo>();
-    if (lane == 0 && n_it > 0) {
+    const bool leader = elect_one();  // the whole warp walks the loop; one lane issues
+    if (n_it > 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(kT, kT, false, false);  // both operands K-major
       constexpr uint32_t idesc_mn = make_idesc_bf16(kT, kT, false, true);   // B operand MN-major
       const uint64_t r1d = make_smem_desc(smem_u32(sR1), 16, 1024), r2d = make_smem_desc(smem_u32(sR2), 16, 1024);
@@ -271,43 +273,47 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       // T1 = R1 X1^T, T2 = R2 X2^T
       auto gemm_t1 = [&](uint64_t xd) {
-        if constexpr (MODE == kDq) gemm_tk(t1, tmem_base + kColR1, xd, idesc_kk); else gemm_ss(t1, r1d, xd, idesc_kk);
+        if constexpr (MODE == kDq) gemm_tk(t1, tmem_base + kColR1, xd, idesc_kk, leader);
+        else gemm_ss(t1, r1d, xd, idesc_kk, leader);
       };
       auto gemm_t2 = [&](uint64_t xd) {
-        if constexpr (MODE == kDq) gemm_tk(t2, tmem_base + kColR2, xd, idesc_kk); else gemm_ss(t2, r2d, xd, idesc_kk);
+        if constexpr (MODE == kDq) gemm_tk(t2, tmem_base + kColR2, xd, idesc_kk, leader);
+        else gemm_ss(t2, r2d, xd, idesc_kk, leader);
       };
       mbar_wait(&x_full[0], 0, ctl, 0x300);
       tc_fence_after_sync();
       gemm_t1(x1k[0]);
-      umma_commit(t1_full);
+      if (leader) umma_commit(t1_full);
       mbar_wait(&x2_full[0], 0, ctl, 0x380);
       tc_fence_after_sync();
       gemm_t2(x2k[0]);
-      umma_commit(t2_full);
-      if constexpr (MODE == kDq) umma_commit(&x2_empty[0]);  // V_0 is only read by dP(0)
+      if (leader) umma_commit(t2_full);
+      if constexpr (MODE == kDq) {
+        if (leader) umma_commit(&x2_empty[0]);  // V_0 is only read by dP(0)
+      }
       for (int k = 0; k < n_it; ++k) {
         const int s = k & 1, sn = s ^ 1;
         const bool more = k + 1 < n_it;
         if constexpr (MODE == kDkDv) {
           mbar_wait(p_full, k & 1, ctl, 0x400);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t1, s ? x2m[1] : x2m[0], idesc_mn, k > 0);  // dV += P^T dO_i
-          umma_commit(&x2_empty[s]);  // last use of dO_i
+          gemm_ts(tmem_base + kColAcc, t1, s ? x2m[1] : x2m[0], idesc_mn, k > 0, leader);  // dV += P^T dO_i
+          if (leader) umma_commit(&x2_empty[s]);  // last use of dO_i
           if (more) {
             mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
             tc_fence_after_sync();
             gemm_t1(sn ? x1k[1] : x1k[0]);  // S^T(k+1)
-            umma_commit(t1_full);
+            if (leader) umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc2, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0);  // dK += dS^T Q_i
-          umma_commit(&x_empty[s]);
+          gemm_ts(tmem_base + kColAcc2, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0, leader);  // dK += dS^T Q_i
+          if (leader) umma_commit(&x_empty[s]);
           if (more) {
             mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
             tc_fence_after_sync();
             gemm_t2(sn ? x2k[1] : x2k[0]);  // dP^T(k+1)
-            umma_commit(t2_full);
+            if (leader) umma_commit(t2_full);
           }
         } else {
           if (more) {
@@ -315,22 +321,22 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_wait(p_full, k & 1, ctl, 0x400);  // T1 of iteration k has been read
             tc_fence_after_sync();
             gemm_t1(sn ? x1k[1] : x1k[0]);  // S(k+1)
-            umma_commit(t1_full);
+            if (leader) umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0);  // dQ += dS K_j
-          umma_commit(&x_empty[s]);
+          gemm_ts(tmem_base + kColAcc, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0, leader);  // dQ += dS K_j
+          if (leader) umma_commit(&x_empty[s]);
           if (more) {
             mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
             tc_fence_after_sync();
             gemm_t2(sn ? x2k[1] : x2k[0]);  // dP(k+1)
-            umma_commit(t2_full);
-            umma_commit(&x2_empty[sn]);  // V_j is only read by dP
+            if (leader) umma_commit(t2_full);
+            if (leader) umma_commit(&x2_empty[sn]);  // V_j is only read by dP
           }
         }
       }
-      umma_commit(acc_full);
+      if (leader) umma_commit(acc_full);
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ compute

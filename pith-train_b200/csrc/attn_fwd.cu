@@ -38,22 +38,24 @@ struct FwdSmem {
 // S[128 x BN] = Q_tile[128 x DQK] * K_blk[BN x DQK]^T, both operands K-major in shared memory.
 // qdesc / kdesc describe the first [rows][64] sub-tile; later K-steps only move the start address.
 template <int DQK, int BN>
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t qdesc, uint64_t kdesc, uint32_t idesc) {
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t qdesc, uint64_t kdesc, uint32_t idesc, bool leader) {
 #pragma unroll
   for (int kk = 0; kk < DQK / 16; ++kk) {
     const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-    umma_ss(d_tmem, desc_advance(qdesc, sub * (kBM * 128) + off), desc_advance(kdesc, sub * (BN * 128) + off), idesc,
-            kk > 0 ? 1u : 0u);
+    if (leader)
+      umma_ss(d_tmem, desc_advance(qdesc, sub * (kBM * 128) + off), desc_advance(kdesc, sub * (BN * 128) + off), idesc,
+              kk > 0 ? 1u : 0u);
   }
 }
 
 // O[128 x 128] (+)= P[128 x BN] (bf16 in TMEM) * V_blk[BN x 128] (MN-major in shared memory:
 // two [BN][64] column blocks, BN * 128 bytes apart).
 template <int BN>
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint64_t vdesc, uint32_t idesc, bool acc) {
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint64_t vdesc, uint32_t idesc, bool acc,
+                                         bool leader) {
 #pragma unroll
   for (int kk = 0; kk < BN / 16; ++kk)
-    umma_ts(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
+    if (leader) umma_ts(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
 }
 
 template <int DQK, int BN, int KST, int VST>
@@ -154,7 +156,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     setmaxnreg_dec<kFwdRegsLo>();
-    if (lane == 0 && nmax > 0) {
+    const bool leader = elect_one();  // the whole warp walks the loop; one lane issues
+    if (nmax > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(kBM, BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(kBM, kDV, false, true);
       uint64_t qd[2], kd[KST], vd[VST];
@@ -170,11 +173,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (nblk[t] > 0) {
-          issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[0], idesc_qk);
-          umma_commit(&s_full[t]);
+          issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[0], idesc_qk, leader);
+          if (leader) umma_commit(&s_full[t]);
         }
       }
-      umma_commit(&k_empty[0]);
+      if (leader) umma_commit(&k_empty[0]);
       for (int j = 0; j < nmax; ++j) {
         const int vs = j % VST;
         const bool have_next = j + 1 < nmax;
@@ -186,17 +189,17 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           if (j < nblk[t]) {
             mbar_wait(&p_full[t], j & 1, ctl, 0x600 + t);
             tc_fence_after_sync();
-            issue_pv<BN>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0);
+            issue_pv<BN>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0, leader);
             if (j + 1 < nblk[t]) {
-              issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk);
-              umma_commit(&s_full[t]);
+              issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk, leader);
+              if (leader) umma_commit(&s_full[t]);
             } else {
-              umma_commit(&o_full[t]);
+              if (leader) umma_commit(&o_full[t]);
             }
           }
         }
-        umma_commit(&v_empty[vs]);
-        if (have_next) umma_commit(&k_empty[ks]);
+        if (leader) umma_commit(&v_empty[vs]);
+        if (have_next) if (leader) umma_commit(&k_empty[ks]);
       }
     }
   } else if (warp >= 4) {

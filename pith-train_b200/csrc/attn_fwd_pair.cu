@@ -39,21 +39,23 @@ struct FwdPairSmem {
 // S[256 x 128] = Q[256 x DQK] K_blk[128 x DQK]^T over the pair. Per CTA: Q tile = DQK/64 sub-tiles of
 // [128][64] (16 KB apart), K half = DQK/64 sub-tiles of [64][64] (8 KB apart), all K-major, 128-byte swizzle.
 template <int DQK>
-__device__ __forceinline__ void issue_qk_pair(uint32_t d_tmem, uint64_t qdesc, uint64_t kdesc, uint32_t idesc) {
+__device__ __forceinline__ void issue_qk_pair(uint32_t d_tmem, uint64_t qdesc, uint64_t kdesc, uint32_t idesc,
+                                              bool leader) {
 #pragma unroll
   for (int kk = 0; kk < DQK / 16; ++kk) {
     const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
-    umma_ss_pair(d_tmem, desc_advance(qdesc, sub * (kBM * 128) + off),
-                 desc_advance(kdesc, sub * ((kPairBN / 2) * 128) + off), idesc, kk > 0 ? 1u : 0u);
+    if (leader)
+      umma_ss_pair(d_tmem, desc_advance(qdesc, sub * (kBM * 128) + off),
+                   desc_advance(kdesc, sub * ((kPairBN / 2) * 128) + off), idesc, kk > 0 ? 1u : 0u);
   }
 }
 // O[256 x 128] (+)= P[256 x 128] (bf16 in each CTA's TMEM) V_blk[128 x 128]; per CTA V half = [128 keys][64 columns]
 // MN-major (one 64-wide column block), 16 keys = 2048 bytes per K-step.
 __device__ __forceinline__ void issue_pv_pair(uint32_t d_tmem, uint32_t p_tmem, uint64_t vdesc, uint32_t idesc,
-                                              bool acc) {
+                                              bool acc, bool leader) {
 #pragma unroll
   for (int kk = 0; kk < kPairBN / 16; ++kk)
-    umma_ts_pair(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
+    if (leader) umma_ts_pair(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
 }
 
 template <int DQK, int KST, int VST>
@@ -160,7 +162,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (rank 0 only)
     setmaxnreg_dec<kFwdRegsLo>();
-    if (rank == 0 && lane == 0 && nmax > 0) {
+    const bool leader = elect_one();  // the whole warp walks the loop; one lane issues
+    if (rank == 0 && nmax > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(2 * kBM, BN, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(2 * kBM, kDV, false, true);
       uint64_t qd[2], kd[KST], vd[VST];
@@ -176,11 +179,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (nblk[t] > 0) {
-          issue_qk_pair<DQK>(tmem_base + t * 128, qd[t], kd[0], idesc_qk);
-          umma_commit_pair(&s_full[t]);
+          issue_qk_pair<DQK>(tmem_base + t * 128, qd[t], kd[0], idesc_qk, leader);
+          if (leader) umma_commit_pair(&s_full[t]);
         }
       }
-      umma_commit_pair(&k_empty[0]);
+      if (leader) umma_commit_pair(&k_empty[0]);
       for (int j = 0; j < nmax; ++j) {
         const int vs = j % VST;
         const bool have_next = j + 1 < nmax;
@@ -192,17 +195,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
           if (j < nblk[t]) {
             mbar_wait(&p_full[t], j & 1, ctl, 0x600 + t);
             tc_fence_after_sync();
-            issue_pv_pair(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0);
+            issue_pv_pair(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0, leader);
             if (j + 1 < nblk[t]) {
-              issue_qk_pair<DQK>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk);
-              umma_commit_pair(&s_full[t]);
+              issue_qk_pair<DQK>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk, leader);
+              if (leader) umma_commit_pair(&s_full[t]);
             } else {
-              umma_commit_pair(&o_full[t]);
+              if (leader) umma_commit_pair(&o_full[t]);
             }
           }
         }
-        umma_commit_pair(&v_empty[vs]);
-        if (have_next) umma_commit_pair(&k_empty[ks]);
+        if (leader) umma_commit_pair(&v_empty[vs]);
+        if (have_next) if (leader) umma_commit_pair(&k_empty[ks]);
       }
     }
   } else if (warp >= 4) {

@@ -367,6 +367,14 @@ template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+// Elects one lane of a converged warp (the same lane every time). The MMA-issuing warps run their whole loop
+// converged and guard only the tcgen05 instructions with this predicate: descriptor arithmetic then stays
+// warp-uniform, which measured 5 % faster backward passes than branching to a single lane around the loop.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 // Adds a byte offset to the start-address field of a shared-memory descriptor.
 __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
