@@ -218,8 +218,8 @@ def parity_record(dev, kept, local_pos, results, Hq, Hkv, scale, world):
     out, lse, dq, dk, dv = results
     pick = sel.to(dev)[order]
     got = {
-        "o": (out[0][pick][:, qhs].float(), ro), "dq": (dq[0][pick][:, qhs].float(), rdq),
-        "dk": (dk[0][pick][:, kvh].float(), rdk), "dv": (dv[0][pick][:, kvh].float(), rdv),
+        "o": (out.detach()[0][pick][:, qhs].float(), ro), "dq": (dq.detach()[0][pick][:, qhs].float(), rdq),
+        "dk": (dk.detach()[0][pick][:, kvh].float(), rdk), "dv": (dv.detach()[0][pick][:, kvh].float(), rdv),
     }
     rec, ok = {}, True
     for name, (a, b) in got.items():

@@ -10,6 +10,8 @@
  * Conventions
  *  - Every buffer is device memory owned by the caller; the library allocates nothing and
  *    keeps no pointer after the call returns. Calls only enqueue work on `stream`.
+ *    One exception: pith_attn_bwd_noalloc works in a fixed scratch area that is part of the
+ *    library's image on every GPU that loads it (see there).
  *  - Tensors are [B][S][H][D] with the innermost dimension contiguous; strides are given in
  *    ELEMENTS for the b, s and h dimensions. Base pointers and (stride * element size) must
  *    be multiples of 16 bytes. bf16 unless stated.
@@ -18,8 +20,9 @@
  *  - Return value: 0 = enqueued; negative = rejected on the host (pith_last_error() has the
  *    text). Device-side anomalies (a bounded wait that ran out) are written to *status
  *    (a zero-initialised device uint32, optional) as (code << 24 | detail); see pith_status_string.
- *  - Re-entrant; no internal threads; no global mutable state besides a cache of TMA descriptors and, per device,
- *    one side stream with two events used by pith_attn_bwd (created on first use).
+ *  - Re-entrant; no internal threads; no global mutable state besides, per device, one side stream with two
+ *    events used by pith_attn_bwd (created on first use) and the device address of the scratch area of
+ *    pith_attn_bwd_noalloc (looked up on its first call; it does not survive cudaDeviceReset).
  */
 #ifndef PITH_B200_H_
 #define PITH_B200_H_

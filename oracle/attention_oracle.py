@@ -246,4 +246,4 @@ def cosine_error(a: torch.Tensor, b: torch.Tensor) -> float:
     return float(1.0 - torch.dot(a, b) / (a.norm() * b.norm() + 1e-300))
 
 
-__all__ = [name for name in dir() if not name.startswith("_")] + ["math"]
+__all__ = [name for name in dir() if not name.startswith("_")]

@@ -540,9 +540,10 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   std::lock_guard<std::mutex> guard(fj->mu);  // one fork/join sequence at a time: the events are shared
   PITH_CUDA(cudaEventRecord(fj->fork, st));
   PITH_CUDA(cudaStreamWaitEvent(fj->side, fj->fork, 0));
-  if (int rc = launch(kDkDv, st)) return rc;
-  int rc = launch(kDq, fj->side);
-  PITH_CUDA(cudaEventRecord(fj->join, fj->side));  // joined even if the launch was rejected (capture stays valid)
+  // Whatever the launches answer, the side stream is joined back: an enclosing stream capture stays valid.
+  int rc = launch(kDkDv, st);
+  if (rc == kOk) rc = launch(kDq, fj->side);
+  PITH_CUDA(cudaEventRecord(fj->join, fj->side));
   PITH_CUDA(cudaStreamWaitEvent(st, fj->join, 0));
   return rc;
 }

@@ -9,7 +9,8 @@
 // accumulators out of it.
 //
 // The first call on a device looks the area's address up (cudaGetSymbolAddress, with that device current)
-// and remembers it; make that first call before any stream capture begins.
+// and remembers it; make that first call before any stream capture begins. The remembered address belongs to
+// the device's current context: a process that calls cudaDeviceReset must not use this entry point afterwards.
 //
 // Consequences of the shared, static scratch area:
 //  - every GPU that loads the library holds kScratchBytes of device memory until the process exits;
@@ -51,17 +52,30 @@ static int scratch_base(unsigned char** out) {
 
 static size_t round256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
+// sizeof(float) * a * b * c * d rounded up to 256, or SIZE_MAX if that does not fit (so that a huge shape can
+// never wrap around into a small byte count).
+static size_t f32_bytes(int64_t a, int64_t b, int64_t c, int64_t d) {
+  if (a <= 0 || b <= 0 || c <= 0 || d <= 0) return SIZE_MAX;
+  unsigned long long n = sizeof(float);
+  for (int64_t f : {a, b, c, d})
+    if (__builtin_mul_overflow(n, static_cast<unsigned long long>(f), &n)) return SIZE_MAX;
+  if (n > SIZE_MAX - 256) return SIZE_MAX;
+  return round256(static_cast<size_t>(n));
+}
+
 }  // namespace pith
 
 using namespace pith;
 
 extern "C" size_t pith_attn_bwd_noalloc_scratch_bytes(int32_t B, int32_t Sq, int32_t Sk, int32_t Hq, int32_t Hkv,
                                                       int32_t Dqk, int32_t Dv) {
-  const size_t delta = round256(sizeof(float) * static_cast<size_t>(B) * Hq * Sq);
-  const size_t dq = round256(sizeof(float) * static_cast<size_t>(B) * Sq * Hq * Dqk);
-  const size_t dk = round256(sizeof(float) * static_cast<size_t>(B) * Sk * Hkv * Dqk);
-  const size_t dv = round256(sizeof(float) * static_cast<size_t>(B) * Sk * Hkv * Dv);
-  return delta + dq + dk + dv;
+  size_t total = 0;
+  for (size_t part : {f32_bytes(B, Hq, Sq, 1), f32_bytes(B, Sq, Hq, Dqk), f32_bytes(B, Sk, Hkv, Dqk),
+                      f32_bytes(B, Sk, Hkv, Dv)}) {
+    if (part == SIZE_MAX || total > SIZE_MAX - part) return SIZE_MAX;  // invalid or absurdly large: never fits
+    total += part;
+  }
+  return total;
 }
 
 extern "C" int pith_attn_bwd_noalloc(const pith_attn_bwd_noalloc_args* a, void* stream) {
@@ -69,6 +83,23 @@ extern "C" int pith_attn_bwd_noalloc(const pith_attn_bwd_noalloc_args* a, void* 
   PITH_REQUIRE(a->q && a->k && a->v && a->o && a->dout && a->lse && a->dq && a->dk && a->dv, "null tensor pointer");
   PITH_REQUIRE(a->B > 0 && a->Sq > 0 && a->Sk > 0 && a->Hq > 0 && a->Hkv > 0 && a->Dqk > 0 && a->Dv > 0,
                "bad shape B=%d Sq=%d Sk=%d Hq=%d Hkv=%d Dqk=%d Dv=%d", a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->Dqk, a->Dv);
+  // the checks pith_attn_bwd would make, made here before anything is enqueued or the shared area is touched
+  PITH_REQUIRE(a->Hq % a->Hkv == 0, "Hq=%d is not a multiple of Hkv=%d", a->Hq, a->Hkv);
+  PITH_REQUIRE(a->Dv == 128 && (a->Dqk == 128 || a->Dqk == 192),
+               "unsupported head dims Dqk=%d Dv=%d (supported: 128/128 and 192/128)", a->Dqk, a->Dv);
+  PITH_REQUIRE(a->softmax_scale > 0.f, "softmax_scale must be positive");
+  PITH_REQUIRE(a->Hq <= 65535 && a->B <= 65535, "Hq and B must fit a grid dimension");
+  for (const void* ptr : {a->q, a->k, a->v, a->o, a->dout, static_cast<const void*>(a->dq),
+                          static_cast<const void*>(a->dk), static_cast<const void*>(a->dv)})
+    PITH_REQUIRE(aligned16(ptr), "tensor base %p is not 16-byte aligned", ptr);
+  auto strides_ok = [&](const int64_t* st3, int heads) {  // bf16: 8 elements = 16 bytes
+    return st3[1] % 8 == 0 && (heads == 1 || st3[2] % 8 == 0) && (a->B == 1 || st3[0] % 8 == 0);
+  };
+  PITH_REQUIRE(strides_ok(a->q_stride, a->Hq) && strides_ok(a->o_stride, a->Hq) && strides_ok(a->do_stride, a->Hq) &&
+                   strides_ok(a->dq_stride, a->Hq) && strides_ok(a->k_stride, a->Hkv) &&
+                   strides_ok(a->v_stride, a->Hkv) && strides_ok(a->dk_stride, a->Hkv) &&
+                   strides_ok(a->dv_stride, a->Hkv),
+               "strides must be multiples of 16 bytes");
   const size_t need = pith_attn_bwd_noalloc_scratch_bytes(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->Dqk, a->Dv);
   if (need > kScratchBytes)
     return fail(kErrInvalidArg,

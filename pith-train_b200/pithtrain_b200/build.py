@@ -6,6 +6,7 @@ The library is written next to this file so that it travels with the source tree
 
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -31,11 +32,6 @@ NVCC_FLAGS = [
 ]
 
 
-def _extra_flags() -> list[str]:
-    """Extra nvcc flags from PITH_B200_NVCC_FLAGS (e.g. -DPITH_PACKED_F32=1), for experiments."""
-    return os.environ.get("PITH_B200_NVCC_FLAGS", "").split()
-
-
 def _nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
@@ -54,7 +50,7 @@ def _fingerprint() -> str:
     for f in files:
         h.update(f.name.encode())
         h.update(f.read_bytes())
-    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
+    h.update(" ".join(NVCC_FLAGS).encode())
     return h.hexdigest()
 
 
@@ -64,16 +60,31 @@ def is_current() -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
-    """Compiles every kernel for sm_100a and links the shared library. Returns its path."""
+    """Compiles every kernel for sm_100a and links the shared library. Returns its path.
+
+    Safe to call from several processes at once (one rank per GPU all call it): builders take a file lock, look
+    again under the lock, and the finished library is moved into place in one step, so nobody loads a half-written
+    file."""
     if not force and is_current():
         return LIB_PATH
     BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    with open(BUILD_DIR / "lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current():  # another process built it while this one waited
+                return LIB_PATH
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
 
     def compile_one(src: Path) -> Path:
         obj = BUILD_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, *_extra_flags(), *extra, "-I", str(INCLUDE_DIR), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(INCLUDE_DIR), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode != 0:
             sys.stderr.write(f"$ {' '.join(cmd)}\n{r.stdout}{r.stderr}\n")
@@ -83,11 +94,13 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, _sources()))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+    tmp = LIB_PATH.with_name(LIB_PATH.name + f".tmp{os.getpid()}")
+    cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("link of libpith_b200.so failed")
+    os.replace(tmp, LIB_PATH)
     (BUILD_DIR / "fingerprint").write_text(_fingerprint())
     return LIB_PATH
 

@@ -39,6 +39,46 @@ def check_device_status(device=None) -> None:
         raise RuntimeError(f"pith_b200 kernel reported: {text}")
 
 
+# Host mirror of the status word: (pinned int32 tensor, event recorded after the last device-to-host copy).
+_status_mirrors: dict[int, list] = {}
+
+
+def post_status_copy(device=None) -> None:
+    """Enqueues, on the current stream, a copy of the status word into pinned host memory and records an event
+    behind it. Costs one 4-byte copy and no synchronisation; the operators call it when a backward has been
+    enqueued, and ``poll_device_status`` reads the mirror later. Skipped while a stream is being captured."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if torch.cuda.is_current_stream_capturing():
+        return
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    m = _status_mirrors.get(idx)
+    if m is None:
+        m = _status_mirrors[idx] = [torch.zeros(1, dtype=torch.int32).pin_memory(), torch.cuda.Event(), False]
+    elif m[2] and not m[1].query():
+        return  # the previous copy has not landed yet: its value is still to be read
+    m[0].copy_(status_word(device), non_blocking=True)
+    m[1].record(torch.cuda.current_stream(device))
+    m[2] = True
+
+
+def poll_device_status(device=None) -> None:
+    """Raises if a kernel enqueued before the last ``post_status_copy`` reported a device-side anomaly (a bounded
+    wait that gave up), without synchronising: it looks at the host mirror only when its copy has completed.
+    The operators call it on entry, so a training loop that never calls ``check_device_status`` still stops at the
+    next attention call instead of training on the output of kernels that skipped their work."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    m = _status_mirrors.get(idx)
+    if m is None or not m[2] or not m[1].query():
+        return
+    m[2] = False
+    val = int(m[0].item()) & 0xFFFFFFFF
+    if val != 0:
+        status_word(device).zero_()
+        text = _lib.load().pith_status_string(val).decode()
+        raise RuntimeError(f"pith_b200 kernel reported: {text}")
+
+
 def _count(n: int) -> None:
     global launch_count
     launch_count += n
@@ -61,6 +101,12 @@ def _bhs(t: torch.Tensor, name: str) -> I64x2:
     return I64x2(t.stride(0), t.stride(1))
 
 
+def _expect(t, shape, name: str) -> None:
+    """A mismatch would otherwise become a TMA map that reads past the tensor: refuse it here."""
+    if t is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
 def _require_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
@@ -78,6 +124,14 @@ def attn_fwd(q, k, v, softmax_scale: float, causal: bool, causal_offset: int = 0
     _, Sk, Hkv, Dv = v.shape
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise TypeError("q, k, v must be bfloat16")
+    _expect(k, (B, Sk, Hkv, Dqk), "k")
+    _expect(v, (B, Sk, Hkv, Dv), "v")
+    _expect(out, (B, Sq, Hq, Dv), "out")
+    _expect(lse, (B, Hq, Sq), "lse")
+    _expect(prev_o, (B, Sq, Hq, Dv), "prev_o")
+    _expect(prev_lse, (B, Hq, Sq), "prev_lse")
+    if (prev_o is None) != (prev_lse is None):
+        raise ValueError("prev_o and prev_lse must be given together")
     if out is None:
         out = torch.empty((B, Sq, Hq, Dv), dtype=torch.float32 if out_fp32 else torch.bfloat16, device=q.device)
     else:
@@ -111,6 +165,8 @@ def bwd_preprocess(o, dout, delta=None):
     """delta [B,H,S] = rowsum(o * dout); see ``pith_attn_bwd_preprocess``."""
     _require_cuda(o, dout, delta)
     B, S, H, Dv = o.shape
+    _expect(dout, (B, S, H, Dv), "dout")
+    _expect(delta, (B, H, S), "delta")
     if delta is None:
         delta = torch.empty((B, H, S), dtype=torch.float32, device=o.device)
     a = _lib.BwdPreprocessArgs()
@@ -143,6 +199,19 @@ def attn_bwd(q, k, v, dout, lse_log2, delta, softmax_scale: float, causal: bool,
     for t, n in ((dq_acc, "dq_acc"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
         if t is not None and t.dtype != torch.float32:
             raise TypeError(f"{n} must be float32")
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (dout, "dout")):
+        if t.dtype != torch.bfloat16:
+            raise TypeError(f"{n} must be bfloat16")
+    _expect(k, (B, Sk, Hkv, Dqk), "k")
+    _expect(v, (B, Sk, Hkv, Dv), "v")
+    _expect(dout, (B, Sq, Hq, Dv), "dout")
+    _expect(lse_log2, (B, Hq, Sq), "lse")
+    _expect(delta, (B, Hq, Sq), "delta")
+    _expect(dq_acc, (B, Sq, Hq, Dqk), "dq_acc")
+    _expect(dk_acc, (B, Sk, Hkv, Dqk), "dk_acc")
+    _expect(dv_acc, (B, Sk, Hkv, Dv), "dv_acc")
+    if (dk_acc is None) != (dv_acc is None):
+        raise ValueError("dk_acc and dv_acc must be given together")
     a = _lib.AttnBwdArgs()
     a.q, a.k, a.v, a.dout = q.data_ptr(), k.data_ptr(), v.data_ptr(), dout.data_ptr()
     a.lse, a.delta = lse_log2.data_ptr(), delta.data_ptr()

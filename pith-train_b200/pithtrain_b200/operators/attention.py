@@ -20,7 +20,10 @@ def _kernels():
 def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,
                 causal: bool) -> Tuple[torch.Tensor, torch.Tensor]:
     """(O bf16 [B,Sq,Hq,Dv], LSE fp32 log2-domain [B,Hq,Sq])."""
-    return _kernels().attn_fwd(q, k, v, softmax_scale, causal, 0)
+    K = _kernels()
+    if q.is_cuda:  # an anomaly an earlier step reported surfaces here, without a synchronisation
+        K.poll_device_status(q.device)
+    return K.attn_fwd(q, k, v, softmax_scale, causal, 0)
 
 
 @attn_fwd_op.register_fake
@@ -44,9 +47,11 @@ def attn_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tens
     if q.shape[-1] == 128:  # the dQ pass stores its bf16 result directly
         dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
         K.attn_bwd(q, k, v, do, lse, delta, softmax_scale, causal, 0, None, dk, dv, dq_out=dq)
+        K.post_status_copy(q.device)
         return dq, K.cast_to_bf16(dk), K.cast_to_bf16(dv)
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     K.attn_bwd(q, k, v, do, lse, delta, softmax_scale, causal, 0, dq, dk, dv)
+    K.post_status_copy(q.device)
     return K.cast_to_bf16(dq), K.cast_to_bf16(dk), K.cast_to_bf16(dv)
 
 
@@ -79,11 +84,14 @@ def flash_attn_func(q, k, v, dropout_p: float = 0.0, softmax_scale: Optional[flo
                     return_attn_probs: bool = False):
     """Stand-in for ``flash_attn.flash_attn_func`` with the arguments PithTrain uses
     (pithtrain/models/qwen3_30b_a3b.py:424-430: ``softmax_scale=..., causal=True``). GQA by head grouping.
-    Features the kernels do not have raise instead of being ignored.
+    Features the kernels do not have raise instead of being ignored; that includes ``deterministic=True``: dK and
+    dV of a GQA group are summed with fp32 atomics, so their last bits depend on the order of arrival.
+    The LSE the forward op also returns is an internal by-product: no gradient flows through it.
     """
     if dropout_p != 0.0 or tuple(window_size) != (-1, -1) or softcap != 0.0 or alibi_slopes is not None \
-            or return_attn_probs:
-        raise NotImplementedError("pithtrain_b200.flash_attn_func supports softmax_scale and causal only")
+            or return_attn_probs or deterministic:
+        raise NotImplementedError("pithtrain_b200.flash_attn_func supports softmax_scale and causal only "
+                                  "(no dropout, window, softcap, alibi, attention probabilities or deterministic mode)")
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
     o, _ = attn_fwd_op(q, k, v, float(softmax_scale), bool(causal))

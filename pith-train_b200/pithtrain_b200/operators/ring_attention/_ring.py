@@ -29,6 +29,29 @@ import torch.distributed as dist
 from . import sharding as sh
 
 
+# NVTX ranges: one per ring, one per ring step and direction. They nest under whatever range the caller has open, so
+# under DualPipeV a step shows up as "layerNN.stage1_f / ring_attn.f / step3.kv_first_half" (the reference opens
+# "layerNN.stage1_f" and "...stage1_b" around attention at pithtrain/dualpipe/execution.py:71,88,101,111).
+# PITH_B200_NVTX=0 turns them off; they are skipped for CPU tensors.
+_nvtx_enabled = _os.environ.get("PITH_B200_NVTX", "1") != "0"
+nvtx_log: list | None = None  # tests set this to a list to record the range names instead of asking a profiler
+
+
+class _Range:
+    def __init__(self, name: str, on: bool):
+        self.name, self.on = name, on and _nvtx_enabled
+
+    def __enter__(self):
+        if nvtx_log is not None:
+            nvtx_log.append(self.name)
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+
+
 class CudaBlockBackend:
     """Block arithmetic on the sm_100a kernels of ``libpith_b200.so``. CUDA tensors only."""
 
@@ -130,21 +153,21 @@ def ring_forward(backend, comm: RingComm, q, k, v, scale: float, cp_rank: int, c
     acc = torch.empty((B, S, Hq, Dv), dtype=torch.float32, device=q.device)
     cur = 0
     for t in range(cp_size):
-        src = (cp_rank - t) % cp_size
-        reqs = comm.exchange(bufs[cur], bufs[cur ^ 1]) if t < cp_size - 1 else None
-        kc, vc = _views(bufs[cur], nk, k.shape, v.shape)
-        kind = sh.step_kind(sharding, cp_rank, src)
-        if kind == sh.STEP_CAUSAL:  # always step 0: initialises the running (O, LSE)
-            backend.fwd_block(q, kc, vc, scale, True, acc, lse, False)
-        elif kind == sh.STEP_FULL:
-            backend.fwd_block(q, kc, vc, scale, False, acc, lse, True)
-        elif kind == sh.STEP_KV_FIRST_HALF:
-            backend.fwd_block(q, kc[:, :c], vc[:, :c], scale, False, acc, lse, True)
-        elif kind == sh.STEP_Q_SECOND_HALF:
-            backend.fwd_block(q[:, c:], kc, vc, scale, False, acc[:, c:], lse[:, :, c:], True)
-        if reqs is not None:
-            comm.wait(reqs)
-            cur ^= 1
+        kind = sh.step_kind(sharding, cp_rank, (cp_rank - t) % cp_size)
+        with _Range(f"ring_attn.f.step{t}.{kind}", q.is_cuda):
+            reqs = comm.exchange(bufs[cur], bufs[cur ^ 1]) if t < cp_size - 1 else None
+            kc, vc = _views(bufs[cur], nk, k.shape, v.shape)
+            if kind == sh.STEP_CAUSAL:  # always step 0: initialises the running (O, LSE)
+                backend.fwd_block(q, kc, vc, scale, True, acc, lse, False)
+            elif kind == sh.STEP_FULL:
+                backend.fwd_block(q, kc, vc, scale, False, acc, lse, True)
+            elif kind == sh.STEP_KV_FIRST_HALF:
+                backend.fwd_block(q, kc[:, :c], vc[:, :c], scale, False, acc, lse, True)
+            elif kind == sh.STEP_Q_SECOND_HALF:
+                backend.fwd_block(q[:, c:], kc, vc, scale, False, acc[:, c:], lse[:, :, c:], True)
+            if reqs is not None:
+                comm.wait(reqs)
+                cur ^= 1
     return backend.cast(acc).to(q.dtype), lse
 
 
@@ -172,34 +195,36 @@ def ring_backward(backend, comm: RingComm, q, k, v, out, lse, dout, scale: float
     grads = [_ring_buffer(comm, nk + nv, torch.float32, q.device) for _ in range(3)]
     cur = 0
     for t in range(cp_size):
-        src = (cp_rank - t) % cp_size
-        kv_reqs = comm.exchange(bufs[cur], bufs[cur ^ 1]) if t < cp_size - 1 else None
-        local, inbound, done = grads[t % 3], grads[(t + 1) % 3], grads[(t - 1) % 3]
-        # the accumulator finished at the previous step travels on while this step computes
-        g_reqs = comm.exchange(done, inbound) if t > 0 else None
-        local.zero_()
-        kc, vc = _views(bufs[cur], nk, k.shape, v.shape)
-        dkc, dvc = _views(local, nk, k.shape, v.shape)
-        kind = sh.step_kind(sharding, cp_rank, src)
-        if kind == sh.STEP_CAUSAL:
-            backend.bwd_block(q, kc, vc, dout, lse, delta, scale, True, dq_acc, dkc, dvc)
-        elif kind == sh.STEP_FULL:
-            backend.bwd_block(q, kc, vc, dout, lse, delta, scale, False, dq_acc, dkc, dvc)
-        elif kind == sh.STEP_KV_FIRST_HALF:
-            backend.bwd_block(q, kc[:, :c], vc[:, :c], dout, lse, delta, scale, False, dq_acc, dkc[:, :c], dvc[:, :c])
-        elif kind == sh.STEP_Q_SECOND_HALF:
-            backend.bwd_block(q[:, c:], kc, vc, dout[:, c:], lse[:, :, c:], delta[:, :, c:], scale, False,
-                              dq_acc[:, c:], dkc, dvc)
-        if g_reqs is not None:
-            comm.wait(g_reqs)
-            local.add_(inbound)
-        if kv_reqs is not None:
-            comm.wait(kv_reqs)
-            cur ^= 1
+        kind = sh.step_kind(sharding, cp_rank, (cp_rank - t) % cp_size)
+        with _Range(f"ring_attn.b.step{t}.{kind}", q.is_cuda):
+            kv_reqs = comm.exchange(bufs[cur], bufs[cur ^ 1]) if t < cp_size - 1 else None
+            local, inbound, done = grads[t % 3], grads[(t + 1) % 3], grads[(t - 1) % 3]
+            # the accumulator finished at the previous step travels on while this step computes
+            g_reqs = comm.exchange(done, inbound) if t > 0 else None
+            local.zero_()
+            kc, vc = _views(bufs[cur], nk, k.shape, v.shape)
+            dkc, dvc = _views(local, nk, k.shape, v.shape)
+            if kind == sh.STEP_CAUSAL:
+                backend.bwd_block(q, kc, vc, dout, lse, delta, scale, True, dq_acc, dkc, dvc)
+            elif kind == sh.STEP_FULL:
+                backend.bwd_block(q, kc, vc, dout, lse, delta, scale, False, dq_acc, dkc, dvc)
+            elif kind == sh.STEP_KV_FIRST_HALF:
+                backend.bwd_block(q, kc[:, :c], vc[:, :c], dout, lse, delta, scale, False, dq_acc, dkc[:, :c],
+                                  dvc[:, :c])
+            elif kind == sh.STEP_Q_SECOND_HALF:
+                backend.bwd_block(q[:, c:], kc, vc, dout[:, c:], lse[:, :, c:], delta[:, :, c:], scale, False,
+                                  dq_acc[:, c:], dkc, dvc)
+            if g_reqs is not None:
+                comm.wait(g_reqs)
+                local.add_(inbound)
+            if kv_reqs is not None:
+                comm.wait(kv_reqs)
+                cur ^= 1
     # last hop: the accumulator this rank just completed belongs to rank+1; ours arrives from rank-1
     last = grads[(cp_size - 1) % 3]
     home = grads[cp_size % 3]
-    comm.wait(comm.exchange(last, home))
+    with _Range("ring_attn.b.home", q.is_cuda):
+        comm.wait(comm.exchange(last, home))
     dk_acc, dv_acc = _views(home, nk, k.shape, v.shape)
     return backend.cast(dq_acc).to(q.dtype), backend.cast(dk_acc).to(k.dtype), backend.cast(dv_acc).to(v.dtype)
 
@@ -312,6 +337,40 @@ def _make_comm(cp_rank, cp_size, global_ranks, device):
     return comm
 
 
+class RingFunction(torch.autograd.Function):
+    """Causal ring attention as an autograd function, shared by the GQA and the MLA operator (the kernels pick
+    their instantiation from the head dimensions): ``apply(q, k, v, softmax_scale, cp_rank, cp_size,
+    global_ranks[, sharding])``. Mirrors pithtrain/operators/ring_attention/standard.py:69-189 and mla.py:43-149:
+    backward returns one gradient per forward argument."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, *extra):
+        sharding = extra[0] if extra else "contiguous"
+        ctx.n_extra = len(extra)
+        assert k.is_contiguous() and v.is_contiguous(), "ring attention k or v is not contiguous"
+        sh.check_sharding(sharding)
+        if q.is_cuda:  # an anomaly an earlier step reported surfaces here, without a synchronisation
+            from ... import kernels
+            kernels.poll_device_status(q.device)
+        out, lse = ring_forward_auto(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, sharding)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.softmax_scale = softmax_scale
+        ctx.cp_rank, ctx.cp_size, ctx.global_ranks, ctx.sharding = cp_rank, cp_size, global_ranks, sharding
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        dq, dk, dv = ring_backward_auto(q, k, v, out, lse, dout, ctx.softmax_scale, ctx.cp_rank, ctx.cp_size,
+                                        ctx.global_ranks, ctx.sharding)
+        if q.is_cuda:
+            from ... import kernels
+            kernels.post_status_copy(q.device)
+        return (dq, dk, dv, None, None, None, None) + (None,) * ctx.n_extra
+
+
 def _use_graph(q) -> bool:
     return _graphs_enabled and q.is_cuda and not torch.cuda.is_current_stream_capturing()
 
@@ -326,7 +385,8 @@ def ring_forward_auto(q, k, v, scale, cp_rank, cp_size, global_ranks, sharding):
     backend = CudaBlockBackend()
     comm = _make_comm(cp_rank, cp_size, global_ranks, q.device)
     if cp_size == 1 or not _use_graph(q):
-        return ring_forward(backend, comm, q, k, v, scale, cp_rank, cp_size, sharding)
+        with _Range("ring_attn.f", q.is_cuda):
+            return ring_forward(backend, comm, q, k, v, scale, cp_rank, cp_size, sharding)
     key = _key("fwd", (q, k, v), scale, cp_rank, cp_size, global_ranks, sharding)
     g = _graph_cache.get(key)
     if g is None:
@@ -341,7 +401,8 @@ def ring_backward_auto(q, k, v, out, lse, dout, scale, cp_rank, cp_size, global_
     backend = CudaBlockBackend()
     comm = _make_comm(cp_rank, cp_size, global_ranks, q.device)
     if cp_size == 1 or not _use_graph(q):
-        return ring_backward(backend, comm, q, k, v, out, lse, dout, scale, cp_rank, cp_size, sharding)
+        with _Range("ring_attn.b", q.is_cuda):
+            return ring_backward(backend, comm, q, k, v, out, lse, dout, scale, cp_rank, cp_size, sharding)
     key = _key("bwd", (q, k, v, out, lse, dout), scale, cp_rank, cp_size, global_ranks, sharding)
     g = _graph_cache.get(key)
     if g is None:

@@ -11,7 +11,6 @@ import torch
 import torch.distributed as dist
 
 from . import _ring
-from .sharding import check_sharding
 
 
 def _online_softmax_combine_log2(out1, lse1, out2, lse2):
@@ -23,28 +22,14 @@ def _online_softmax_combine_log2(out1, lse1, out2, lse2):
     return kernels.combine(out1, lse1, out2, lse2, natural=False)
 
 
-class RingMLAAttentionFunc(torch.autograd.Function):
-    """Causal ring MLA attention; ``apply(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks[, sharding])``."""
+class RingMLAAttentionFunc(_ring.RingFunction):
+    """Causal ring MLA attention; ``apply(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks[, sharding])``
+    (reference: mla.py:43). Only the wording of the contiguity check differs from the GQA operator."""
 
     @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, *extra):
-        sharding = extra[0] if extra else "contiguous"
-        ctx.n_extra = len(extra)
+    def forward(ctx, q, k, v, *args):
         assert k.is_contiguous() and v.is_contiguous(), "ring MLA attention k or v is not contiguous"
-        check_sharding(sharding)
-        out, lse = _ring.ring_forward_auto(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, sharding)
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.softmax_scale = softmax_scale
-        ctx.cp_rank, ctx.cp_size, ctx.global_ranks, ctx.sharding = cp_rank, cp_size, global_ranks, sharding
-        return out
-
-    @staticmethod
-    def backward(ctx, dout):
-        dout = dout.contiguous()
-        q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = _ring.ring_backward_auto(q, k, v, out, lse, dout, ctx.softmax_scale, ctx.cp_rank, ctx.cp_size,
-                                              ctx.global_ranks, ctx.sharding)
-        return (dq, dk, dv, None, None, None, None) + (None,) * ctx.n_extra
+        return _ring.RingFunction.forward(ctx, q, k, v, *args)
 
 
 def ring_mla_attention_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,

@@ -12,7 +12,6 @@ import torch
 import torch.distributed as dist
 
 from . import _ring
-from .sharding import check_sharding
 
 
 def _ring_send_recv_kv(send_k: torch.Tensor, send_v: torch.Tensor, next_global: int, prev_global: int):
@@ -46,29 +45,9 @@ def _online_softmax_combine(out1, lse1, out2, lse2):
     return kernels.combine(out1, lse1, out2, lse2, natural=True)
 
 
-class RingAttentionFunc(torch.autograd.Function):
-    """Causal ring attention; ``apply(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks[, sharding])``."""
-
-    @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, *extra):
-        sharding = extra[0] if extra else "contiguous"
-        ctx.n_extra = len(extra)
-        assert k.is_contiguous() and v.is_contiguous(), "ring attention k or v is not contiguous"
-        check_sharding(sharding)
-        out, lse = _ring.ring_forward_auto(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks, sharding)
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.softmax_scale = softmax_scale
-        ctx.cp_rank, ctx.cp_size, ctx.global_ranks, ctx.sharding = cp_rank, cp_size, global_ranks, sharding
-        return out
-
-    @staticmethod
-    def backward(ctx, dout):
-        q, k, v, out, lse = ctx.saved_tensors
-        if dout.stride(-1) != 1:
-            dout = dout.contiguous()
-        dq, dk, dv = _ring.ring_backward_auto(q, k, v, out, lse, dout, ctx.softmax_scale, ctx.cp_rank, ctx.cp_size,
-                                              ctx.global_ranks, ctx.sharding)
-        return (dq, dk, dv, None, None, None, None) + (None,) * ctx.n_extra
+class RingAttentionFunc(_ring.RingFunction):
+    """Causal ring attention; ``apply(q, k, v, softmax_scale, cp_rank, cp_size, global_ranks[, sharding])``
+    (reference: standard.py:69)."""
 
 
 def ring_attention_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float,

@@ -62,6 +62,32 @@ def test_schedule_under_pull_exchange(cp, layout):
     _check_against_full(res, cp, layout, q, k, v, do, 0.25, 5e-6)
 
 
+def test_every_ring_step_opens_a_named_range():
+    """One NVTX range per ring step and direction, named by step index and kind, so that a profile of a DualPipeV run
+    shows them nested under the caller's ``layerNN.stage1_f`` / ``stage1_b`` ranges (pithtrain/dualpipe/execution.py:71,101)."""
+    cp, S = 2, 64
+    q, k, v, do = _problem(S, dtype=torch.float64)
+    _ring.nvtx_log = log = []
+    try:
+        ThreadRing(1).run(lambda r, comm: _rank_fwd_bwd(1, cp, _OneRankOfTwo(), "zigzag", q, k, v, do, 0.25, torch.float64))
+    finally:
+        _ring.nvtx_log = None
+    assert log == ["ring_attn.f.step0.causal", "ring_attn.f.step1.kv_first_half",
+                   "ring_attn.b.step0.causal", "ring_attn.b.step1.kv_first_half", "ring_attn.b.home"]
+
+
+class _OneRankOfTwo:
+    """Stand-in communicator for a schedule-only run: the 'received' block is whatever the buffer holds."""
+
+    def exchange(self, send, recv):
+        recv.copy_(send)
+        return None
+
+    @staticmethod
+    def wait(h):
+        return None
+
+
 def test_schedule_mla_shapes_in_process():
     """q/k width 192, v width 128, 16 heads without grouping (the DeepSeek-V2-Lite attention layout)."""
     cp, S = 4, 64

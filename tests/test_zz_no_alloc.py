@@ -1,4 +1,5 @@
-"""The allocation-free attention backward (``pith_attn_bwd_noalloc``) against the regular entry points.
+"""The allocation-free attention backward (``pith_attn_bwd_noalloc``) against the regular entry points and the
+CPU oracle.
 
 Some hosts cannot allocate device memory at the point where the backward runs: their memory pool was frozen
 after start-up, or the runtime they are embedded in owns every device allocation, or they cannot take the
@@ -15,6 +16,7 @@ import pytest
 import torch
 
 from helpers import assert_bf16_close
+from oracle import attention_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -66,12 +68,16 @@ def test_noalloc_backward_matches_regular_entry_points_twice(cuda_device):
         o, lse = K.attn_fwd(q, k, v, scale, causal, 0)
         assert lib.pith_attn_bwd_noalloc_scratch_bytes(B, Sq, Sk, Hq, Hkv, Dqk, 128) <= _lib.NOALLOC_SCRATCH_BYTES
         ref = _regular_backward(K, q, k, v, o, do, lse, scale, causal)
+        # two CUDA paths agreeing is not parity: the oracle (fp32 on the CPU, from its own forward) decides
+        ro, rl = O.attention_fwd(q.cpu(), k.cpu(), v.cpu(), scale, causal, 0)
+        oracle = O.attention_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), rl, O.delta(ro, do.cpu()), scale, causal, 0)
         for call in range(2):
             got = _noalloc_backward(q, k, v, o, do, lse, scale, causal, status)
             torch.cuda.synchronize()
-            for name, a, b in zip(("dQ", "dK", "dV"), got, ref):
+            for name, a, b, c in zip(("dQ", "dK", "dV"), got, ref, oracle):
                 # same kernels, same inputs; only the order of the fp32 atomic additions may differ
-                assert_bf16_close(a, b, f"{name} (call {call})")
+                assert_bf16_close(a, b, f"{name} vs regular entry points (call {call})")
+                assert_bf16_close(a, c, f"{name} vs oracle (call {call})")
     K.check_device_status(cuda_device)
 
 
@@ -87,3 +93,11 @@ def test_noalloc_rejects_problems_beyond_the_scratch_area(cuda_device):
     assert lib.pith_attn_bwd_noalloc(ctypes.byref(a), None) < 0
     msg = lib.pith_last_error().decode()
     assert "scratch" in msg and str(_lib.NOALLOC_SCRATCH_BYTES) in msg
+    # a shape whose byte count would wrap around 64 bits is "does not fit", not a small number
+    huge = lib.pith_attn_bwd_noalloc_scratch_bytes(65535, 2 ** 31 - 1, 2 ** 31 - 1, 65535, 1, 192, 128)
+    assert huge > _lib.NOALLOC_SCRATCH_BYTES
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv = 65535, 2 ** 31 - 1, 2 ** 31 - 1, 65535, 1
+    assert lib.pith_attn_bwd_noalloc(ctypes.byref(a), None) < 0 and "scratch" in lib.pith_last_error().decode()
+    # checks of the regular entry point are made before the shared area is touched
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.Dqk = 1, 128, 128, 4, 4, 96
+    assert lib.pith_attn_bwd_noalloc(ctypes.byref(a), None) < 0 and "head dims" in lib.pith_last_error().decode()
