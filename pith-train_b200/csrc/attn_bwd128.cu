@@ -36,7 +36,12 @@ constexpr int kRegsLo = 72;
 constexpr int kRegsHi = 208;
 constexpr int kT = 128;             // tile edge (rows of both tiles, head dimension)
 constexpr int kTile = kT * kT * 2;  // bytes of one bf16 tile
-constexpr int kNST = 2;
+constexpr int kNST = 2;   // stages of each streamed-tile ring that have shared memory of their own
+constexpr int kNSTQ = 3;  // mode kDq: one more stage per ring in the resident tiles' shared memory, which is free once
+                          // they have been copied into TMEM. K_j is read first by S(j) and last by dQ(j), so a stage
+                          // is held for a whole iteration and a two-deep ring leaves the next load (a TMA round trip
+                          // of ~2000 cycles) no time before S(j+1) wants it.
+constexpr int kMaxST = 3;
 
 struct Smem {
   static constexpr int kR1Off = 0;
@@ -45,7 +50,7 @@ struct Smem {
   static constexpr int kX2Off = kX1Off + kNST * kTile;
   static constexpr int kStatOff = kX2Off + kNST * kTile;  // [kNST][2][128] floats
   static constexpr int kBarOff = kStatOff + kNST * 2 * kT * 4;
-  static constexpr int kNumBars = 1 + 4 * kNST + 6;
+  static constexpr int kNumBars = 1 + 4 * kMaxST + 6;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;
 };
@@ -109,15 +114,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* sX1 = smem + Smem::kX1Off;
   uint8_t* sX2 = smem + Smem::kX2Off;
   float* sStat = reinterpret_cast<float*>(smem + Smem::kStatOff);
+  constexpr int NS = (MODE == kDq) ? kNSTQ : kNST;  // ring depth of this mode
+  auto x1_stage = [&](int st) { return st < kNST ? sX1 + st * kTile : sR1; };
+  auto x2_stage = [&](int st) { return st < kNST ? sX2 + st * kTile : sR2; };
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBarOff);
   uint64_t* res_full = bars;
   // The two streamed tiles have separate rings: X2 (dO_i / V_j) is last used earlier than X1 (Q_i / K_j), so
   // its next load can start earlier, and the GEMM that needs X1 does not wait for X2's bytes.
   uint64_t* x_full = bars + 1;          // X1 (+ statistics in kDkDv)
-  uint64_t* x_empty = x_full + kNST;
-  uint64_t* x2_full = x_empty + kNST;
-  uint64_t* x2_empty = x2_full + kNST;
-  uint64_t* t1_full = x2_empty + kNST;
+  uint64_t* x_empty = x_full + kMaxST;
+  uint64_t* x2_full = x_empty + kMaxST;
+  uint64_t* x2_empty = x2_full + kMaxST;
+  uint64_t* t1_full = x2_empty + kMaxST;
   uint64_t* t2_full = t1_full + 1;
   uint64_t* p_full = t2_full + 1;   // kDkDv: P^T is in TMEM; kDq: T1 has been read
   uint64_t* ds_full = p_full + 1;   // dS is in TMEM
@@ -153,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // a launch that finds an error already recorded (by an earlier CTA or launch) does no work
     *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) ? 1u : 0u;
     mbar_init(res_full, 1);
-    for (int i = 0; i < kNST; ++i) {
+    for (int i = 0; i < kMaxST; ++i) {
       mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
       mbar_init(&x_empty[i], 1);
       mbar_init(&x2_full[i], 1);
@@ -215,19 +223,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       };
       auto step = [&](int k, float (&rl)[4], float (&rd)[4]) {
-        const int s = k % kNST;
+        const int s = k % NS;
         const int x0 = (it_begin + k) * kT;
         if (lane == 0) {
-          mbar_wait(&x_empty[s], ((k / kNST) & 1) ^ 1, ctl, 0x100 + s);
+          if (MODE == kDq && k == kNST) mbar_wait(rt_full, 0, ctl, 0x1F0);  // the resident tiles' memory is free now
+          mbar_wait(&x_empty[s], ((k / NS) & 1) ^ 1, ctl, 0x100 + s);
           mbar_arrive_expect_tx(&x_full[s], kTile);
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub)
-            tma_load_4d(sX1 + s * kTile + sub * (kT * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
-          mbar_wait(&x2_empty[s], ((k / kNST) & 1) ^ 1, ctl, 0x180 + s);
+            tma_load_4d(x1_stage(s) + sub * (kT * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
+          mbar_wait(&x2_empty[s], ((k / NS) & 1) ^ 1, ctl, 0x180 + s);
           mbar_arrive_expect_tx(&x2_full[s], kTile);
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub)
-            tma_load_4d(sX2 + s * kTile + sub * (kT * 128), &tm_x2, &x2_full[s], sub * 64, x_head, x0, batch);
+            tma_load_4d(x2_stage(s) + sub * (kT * 128), &tm_x2, &x2_full[s], sub * 64, x_head, x0, batch);
         }
         __syncwarp();  // the stage is free (lane 0 saw x_empty) before anyone writes its statistics
         if constexpr (MODE == kDkDv) {
@@ -257,14 +266,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_kk = make_idesc_bf16(kT, kT, false, false);  // both operands K-major
       constexpr uint32_t idesc_mn = make_idesc_bf16(kT, kT, false, true);   // B operand MN-major
       const uint64_t r1d = make_smem_desc(smem_u32(sR1), 16, 1024), r2d = make_smem_desc(smem_u32(sR2), 16, 1024);
-      uint64_t x1k[kNST], x2k[kNST], x1m[kNST], x2m[kNST];
+      uint64_t x1k[NS], x2k[NS], x1m[NS], x2m[NS];
 #pragma unroll
-      for (int s = 0; s < kNST; ++s) {
-        x1k[s] = make_smem_desc(smem_u32(sX1) + s * kTile, 16, 1024);
-        x2k[s] = make_smem_desc(smem_u32(sX2) + s * kTile, 16, 1024);
-        x1m[s] = make_smem_desc(smem_u32(sX1) + s * kTile, kT * 128, 1024);
-        x2m[s] = make_smem_desc(smem_u32(sX2) + s * kTile, kT * 128, 1024);
+      for (int s = 0; s < NS; ++s) {
+        x1k[s] = make_smem_desc(smem_u32(x1_stage(s)), 16, 1024);
+        x2k[s] = make_smem_desc(smem_u32(x2_stage(s)), 16, 1024);
+        x1m[s] = make_smem_desc(smem_u32(x1_stage(s)), kT * 128, 1024);
+        x2m[s] = make_smem_desc(smem_u32(x2_stage(s)), kT * 128, 1024);
       }
+      // register selects instead of runtime-indexed arrays (which would live in local memory)
+      auto pick = [](const uint64_t (&d)[NS], int st) { return st == 0 ? d[0] : (st == 1 || NS == 2) ? d[1] : d[NS - 1]; };
       const uint32_t t1 = tmem_base + kColT1, t2 = tmem_base + kColT2;
       if constexpr (MODE == kDq) {
         mbar_wait(rt_full, 0, ctl, 0x210);
@@ -292,45 +303,46 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (leader) umma_commit(&x2_empty[0]);  // V_0 is only read by dP(0)
       }
       for (int k = 0; k < n_it; ++k) {
-        const int s = k & 1, sn = s ^ 1;
+        const int s = k % NS, sn = (k + 1) % NS;                       // stages of iterations k and k + 1
+        const uint32_t ph_n = static_cast<uint32_t>((k + 1) / NS) & 1u;  // phase of stage sn's "full" barrier
         const bool more = k + 1 < n_it;
         if constexpr (MODE == kDkDv) {
           mbar_wait(p_full, k & 1, ctl, 0x400);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t1, s ? x2m[1] : x2m[0], idesc_mn, k > 0, leader);  // dV += P^T dO_i
+          gemm_ts(tmem_base + kColAcc, t1, pick(x2m, s), idesc_mn, k > 0, leader);  // dV += P^T dO_i
           if (leader) umma_commit(&x2_empty[s]);  // last use of dO_i
           if (more) {
-            mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
+            mbar_wait(&x_full[sn], ph_n, ctl, 0x300 + sn);
             tc_fence_after_sync();
-            gemm_t1(sn ? x1k[1] : x1k[0]);  // S^T(k+1)
+            gemm_t1(pick(x1k, sn));  // S^T(k+1)
             if (leader) umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc2, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0, leader);  // dK += dS^T Q_i
+          gemm_ts(tmem_base + kColAcc2, t2, pick(x1m, s), idesc_mn, k > 0, leader);  // dK += dS^T Q_i
           if (leader) umma_commit(&x_empty[s]);
           if (more) {
-            mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
+            mbar_wait(&x2_full[sn], ph_n, ctl, 0x380 + sn);
             tc_fence_after_sync();
-            gemm_t2(sn ? x2k[1] : x2k[0]);  // dP^T(k+1)
+            gemm_t2(pick(x2k, sn));  // dP^T(k+1)
             if (leader) umma_commit(t2_full);
           }
         } else {
           if (more) {
-            mbar_wait(&x_full[sn], ((k + 1) >> 1) & 1, ctl, 0x300 + sn);
+            mbar_wait(&x_full[sn], ph_n, ctl, 0x300 + sn);
             mbar_wait(p_full, k & 1, ctl, 0x400);  // T1 of iteration k has been read
             tc_fence_after_sync();
-            gemm_t1(sn ? x1k[1] : x1k[0]);  // S(k+1)
+            gemm_t1(pick(x1k, sn));  // S(k+1)
             if (leader) umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t2, s ? x1m[1] : x1m[0], idesc_mn, k > 0, leader);  // dQ += dS K_j
+          gemm_ts(tmem_base + kColAcc, t2, pick(x1m, s), idesc_mn, k > 0, leader);  // dQ += dS K_j
           if (leader) umma_commit(&x_empty[s]);
           if (more) {
-            mbar_wait(&x2_full[sn], ((k + 1) >> 1) & 1, ctl, 0x380 + sn);
+            mbar_wait(&x2_full[sn], ph_n, ctl, 0x380 + sn);
             tc_fence_after_sync();
-            gemm_t2(sn ? x2k[1] : x2k[0]);  // dP(k+1)
+            gemm_t2(pick(x2k, sn));  // dP(k+1)
             if (leader) umma_commit(t2_full);
             if (leader) umma_commit(&x2_empty[sn]);  // V_j is only read by dP
           }
@@ -367,9 +379,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     for (int k = 0; k < n_it; ++k) {
-      const int s = k & 1;
+      const int s = k % kNST;  // statistics stage (mode kDkDv, two-deep ring)
       const int x0 = (it_begin + k) * kT + h * 64;  // global position of this thread's first column
-      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k >> 1) & 1, ctl, 0x600 + s);
+      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k / kNST) & 1, ctl, 0x600 + s);
       const ulonglong2* st_l = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 0) * kT + h * 64);
       const ulonglong2* st_d = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 1) * kT + h * 64);
       // key n visible to query m iff n <= m + off
