@@ -201,3 +201,83 @@ def test_deepseek_attention_layer_with_the_import_swap(ref, cuda_device):
     finally:
         layer.attn = original
     _compare_layers(stock, swapped, "DeepseekV2LiteAttention")
+
+
+# ----------------------------------------------------------------------------- zigzag through the reference's caller
+def _cp_layer_worker(rank, world, port, path, ref_dir):
+    """One CP rank: the reference's Qwen3MoeAttention with a CP group, its `ring_attention_func` replaced by this
+    library's with zigzag sharding, fed the zigzag slice of the hidden states and zigzag position ids."""
+    import os
+    import torch.distributed as dist
+    sys.path.insert(0, ref_dir)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import pithtrain.models.qwen3_30b_a3b as M
+        from pithtrain_b200.modules.distributed import cp_position_ids
+        from pithtrain_b200.operators.ring_attention import ring_attention_func, sharding as sh
+        group = dist.new_group(list(range(world)))
+        M.ring_attention_func = lambda q, k, v, softmax_scale, cp_group: ring_attention_func(  # the import swap
+            q, k, v, softmax_scale, cp_group, "zigzag")
+        torch.manual_seed(0)
+        layer = M.Qwen3MoeAttention(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                    cp_group=group).to(dev).bfloat16()
+        assert layer.use_ring_attn
+        S = 1024 * world
+        g = torch.Generator().manual_seed(7)
+        x = torch.randn(1, S, 512, generator=g).bfloat16()
+        dout = torch.randn(1, S, 512, generator=g).bfloat16()
+        xl = sh.shard_sequence(x, world, rank, "zigzag").contiguous().to(dev).requires_grad_()
+        dl = sh.shard_sequence(dout, world, rank, "zigzag").contiguous().to(dev)
+        pos = cp_position_ids(S // world, rank, world, "zigzag", device=dev)[0].float()
+        inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, device=dev, dtype=torch.float32) / 128))
+        emb = torch.outer(pos, inv).repeat(1, 2)[None]
+        out = layer(xl, (emb.cos().bfloat16(), emb.sin().bfloat16()))
+        out.backward(dl)
+        torch.cuda.synchronize()
+        grads = {n: p.grad.detach().float() for n, p in layer.named_parameters()}
+        for t in grads.values():  # what FSDP / DDP would do across the CP ranks
+            dist.all_reduce(t)
+        torch.save({"out": out.detach().cpu(), "dx": xl.grad.cpu(), "grads": {n: t.cpu() for n, t in grads.items()}},
+                   os.path.join(path, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reference_layer_under_zigzag_cp_equals_single_gpu(ref, cuda_device, tmp_path):
+    """Config-3 plumbing through a real caller (pithtrain/models/qwen3_30b_a3b.py:432): the reference's attention layer
+    on 2+ GPUs with zigzag token slices, zigzag position ids and this library's ring operator must reproduce the same
+    layer on one GPU with its stock flash-attn path over the whole sequence."""
+    import socket
+    import torch.multiprocessing as mp
+    from pithtrain_b200.operators.ring_attention import sharding as sh
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_cp_layer_worker, args=(world, port, str(tmp_path), str(ref)), nprocs=world, join=True)
+    res = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    import pithtrain.models.qwen3_30b_a3b as M
+    torch.manual_seed(0)
+    layer = M.Qwen3MoeAttention(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128)
+    layer = layer.to(cuda_device).bfloat16()
+    S = 1024 * world
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(1, S, 512, generator=g).bfloat16().to(cuda_device).requires_grad_()
+    dout = torch.randn(1, S, 512, generator=g).bfloat16().to(cuda_device)
+    inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, device=cuda_device, dtype=torch.float32) / 128))
+    emb = torch.outer(torch.arange(S, device=cuda_device, dtype=torch.float32), inv).repeat(1, 2)[None]
+    out = layer(x, (emb.cos().bfloat16(), emb.sin().bfloat16()))  # stock: flash_attn_func over the whole sequence
+    out.backward(dout)
+    got_out = sh.unshard_sequence([r["out"] for r in res], "zigzag", seq_dim=1)
+    got_dx = sh.unshard_sequence([r["dx"] for r in res], "zigzag", seq_dim=1)
+    assert_bf16_close(got_out, out.detach(), "layer output, zigzag CP vs single GPU")
+    assert O.cosine_error(got_out, out.detach().cpu()) < 1e-4
+    assert O.cosine_error(got_dx, x.grad.cpu()) < 1e-4
+    for n, p in layer.named_parameters():
+        assert O.cosine_error(res[0]["grads"][n], p.grad.float().cpu()) < 1e-4, n
