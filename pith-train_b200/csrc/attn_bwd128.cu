@@ -419,7 +419,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int j = i + 2 * u;
           float a0, a1;
           f2_unpack(f2_fma(f2_pack(__uint_as_float(pv[j]), __uint_as_float(pv[j + 1])), c2, nl2[u]), a0, a1);
-          float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+          float p0, p1;
+          if (MODE == kDq && ((j >> 1) & 3) == 0 && my_lse != INFINITY) {  // dQ pass: every fourth pair on the FMA
+                                                                            // pipe; rows without keys keep exact zeros
+            exp2_poly2(a0, a1, p0, p1);
+          } else {
+            p0 = fast_exp2(a0);
+            p1 = fast_exp2(a1);
+          }
           if (need_mask) {
             if constexpr (MODE == kDkDv) {
               if (j < lim) p0 = 0.f;

@@ -353,6 +353,27 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+// 2^x for a pair of floats on the FMA pipe instead of the MUFU: x = n + f with n = round(x), |f| <= 0.5, 2^f by a
+// degree-3 polynomial (relative error below 8e-5, far inside the bf16 rounding the results get), n added to the
+// exponent field. Inputs are clamped to >= -125 (the result stays a normal number, about 2e-38): callers that need an
+// exact 0 for -inf (masked scores, rows without any visible key) must take the MUFU path for those. The kernels route
+// a quarter of their exponentials through it where the softmax threads are the critical resource (measured: forward
+// and dQ pass 3 % faster at 25 %, slower at 50 %; no effect in the dK/dV pass).
+__device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
+  const uint64_t x2 = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t magic = f2_pack(12582912.f, 12582912.f), nmagic = f2_pack(-12582912.f, -12582912.f);  // 1.5 * 2^23
+  const uint64_t xi = f2_add(x2, magic);  // low mantissa bits = round(x)
+  const uint64_t fr = f2_fma(f2_add(xi, nmagic), f2_pack(-1.f, -1.f), x2);
+  uint64_t p = f2_fma(f2_pack(0.05508868396282196f, 0.05508868396282196f), fr,
+                      f2_pack(0.24260404706001282f, 0.24260404706001282f));
+  p = f2_fma(p, fr, f2_pack(0.6932762265205383f, 0.6932762265205383f));
+  p = f2_fma(p, fr, f2_pack(0.9999289512634277f, 0.9999289512634277f));
+  float a0, a1, n0, n1;
+  f2_unpack(p, a0, a1);
+  f2_unpack(xi, n0, n1);
+  p0 = __int_as_float(__float_as_int(a0) + (__float_as_int(n0) << 23));
+  p1 = __int_as_float(__float_as_int(a1) + (__float_as_int(n1) << 23));
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
