@@ -24,6 +24,8 @@
 // TMEM columns: T1 [0,128), T2 [128,256), accumulators [256,384) (dV or dQ) and [384,512) (dK).
 // The packed bf16 operands overlay the first half of each thread's own 64 score columns:
 // queries/keys 0..63 at columns [0,32), 64..127 at [64,96) of T1 (P^T) / T2 (dS).
+#include <type_traits>
+
 #include "attn_bwd_common.h"
 #include "common.cuh"
 #include "host_common.h"
@@ -369,6 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     const uint64_t my_nl2 = f2_pack(-my_lse, -my_lse), my_nd2 = f2_pack(-my_delta, -my_delta);
+    const bool emu_ok = __all_sync(0xFFFFFFFFu, my_lse != INFINITY);  // warp-uniform
     if constexpr (MODE == kDq) {
       if (n_it > 0) {  // one-time copy of the resident tiles into TMEM: half 0 takes Q, half 1 takes dO
         mbar_wait(res_full, 0, ctl, 0x220);
@@ -405,6 +408,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_before_sync();
         mbar_arrive(p_full);
       }
+      // Two copies of the loop (a run-time test inside it costs more than it saves): in the dQ pass every fourth pair
+      // of exponentials runs on the FMA pipe unless the warp holds a row without keys, which needs the MUFU's exact 0.
+      auto p_block = [&](auto emu_tag) {
+        constexpr bool EMU = decltype(emu_tag)::value;
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
         uint64_t nl2[2];
@@ -420,8 +427,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           float a0, a1;
           f2_unpack(f2_fma(f2_pack(__uint_as_float(pv[j]), __uint_as_float(pv[j + 1])), c2, nl2[u]), a0, a1);
           float p0, p1;
-          if (MODE == kDq && ((j >> 1) & 3) == 0 && my_lse != INFINITY) {  // dQ pass: every fourth pair on the FMA
-                                                                            // pipe; rows without keys keep exact zeros
+          if (EMU && ((j >> 1) & 3) == 0) {
             exp2_poly2(a0, a1, p0, p1);
           } else {
             p0 = fast_exp2(a0);
@@ -440,6 +446,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           pv[j + 1] = __float_as_uint(p1);
         }
       }
+      };
+      if (MODE == kDq && emu_ok) p_block(std::true_type{});
+      else p_block(std::false_type{});
       if constexpr (MODE == kDkDv) {
         uint32_t pa[32];
 #pragma unroll

@@ -104,14 +104,7 @@ __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const Abort
                                            __uint_as_float(sr[cchunk * 64 + 2 * i + 1])), c2, nmc2);
         float x0, x1;
         f2_unpack(x2, x0, x1);
-        float p0, p1;
-        if ((i & 3) == 0 && !need_mask) {  // every fourth pair on the FMA pipe (the MUFU is what this loop waits
-                                           // for); masked blocks keep the MUFU, whose 2^-inf is exactly 0
-          exp2_poly2(x0, x1, p0, p1);
-        } else {
-          p0 = fast_exp2(x0);
-          p1 = fast_exp2(x1);
-        }
+        const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
         ls2[i & 1] = f2_add(ls2[i & 1], f2_pack(p0, p1));
         pk[i] = pack_bf16(p0, p1);
       }
