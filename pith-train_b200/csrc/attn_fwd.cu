@@ -30,7 +30,7 @@ struct FwdSmem {
   static constexpr int kKOff = kQOff + 2 * kQTile;
   static constexpr int kVOff = kKOff + KST * kKTile;
   static constexpr int kBarOff = kVOff + VST * kVTile;
-  static constexpr int kNumBars = 1 + 2 * KST + 2 * VST + 6;
+  static constexpr int kNumBars = 1 + 2 * KST + 2 * VST + 8;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;  // slack for the 1024-byte alignment of the base
 };
@@ -50,11 +50,12 @@ __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t qdesc, uint64
 
 // O[128 x 128] (+)= P[128 x BN] (bf16 in TMEM) * V_blk[BN x 128] (MN-major in shared memory:
 // two [BN][64] column blocks, BN * 128 bytes apart).
-template <int BN>
+// K-steps [K0, K1) of the block's BN / 16: the first half can run as soon as the first 64 keys' P has been stored.
+template <int K0, int K1>
 __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint64_t vdesc, uint32_t idesc, bool acc,
                                          bool leader) {
 #pragma unroll
-  for (int kk = 0; kk < BN / 16; ++kk)
+  for (int kk = K0; kk < K1; ++kk)
     if (leader) umma_ts(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
 }
 
@@ -77,6 +78,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   uint64_t* s_full = v_empty + VST;  // [2]
   uint64_t* p_full = s_full + 2;     // [2]
   uint64_t* o_full = p_full + 2;     // [2]
+  uint64_t* ph_full = o_full + 2;    // [2] P of the block's first 64 keys is in TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -110,7 +112,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     mbar_init(q_full, 1);
     for (int i = 0; i < KST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < VST; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); mbar_init(&ph_full[t], 128); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -187,9 +189,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < nblk[t]) {
+            mbar_wait(&ph_full[t], j & 1, ctl, 0x680 + t);
+            tc_fence_after_sync();
+            issue_pv<0, BN / 32>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0, leader);
             mbar_wait(&p_full[t], j & 1, ctl, 0x600 + t);
             tc_fence_after_sync();
-            issue_pv<BN>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0, leader);
+            issue_pv<BN / 32, BN / 16>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, true, leader);
             if (j + 1 < nblk[t]) {
               issue_qk<DQK, BN>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk, leader);
               if (leader) umma_commit(&s_full[t]);
@@ -212,8 +217,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const uint32_t tS = tmem_base + lane_addr + t * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
     uint64_t* pf = &p_full[t];
-    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf] { mbar_arrive(pf); }, tS, tO, m0 + t * kBM, row, nblk[t],
-                         head, batch, t);
+    uint64_t* ph = &ph_full[t];
+    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf] { mbar_arrive(pf); }, [ph] { mbar_arrive(ph); }, tS, tO,
+                         m0 + t * kBM, row, nblk[t], head, batch, t);
   } else {
     setmaxnreg_dec<kFwdRegsLo>();  // warps 2 and 3 only give their registers away
   }

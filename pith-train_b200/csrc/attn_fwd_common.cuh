@@ -39,11 +39,14 @@ int launch_fwd_pair(const pith_attn_fwd_args* a, const FwdParams& p, cudaStream_
 // One softmax warpgroup: thread = query row = TMEM lane. Walks the `nb` score tiles of its query tile
 // (S at tS, 128 fp32 columns, P written back over its first 64 columns as packed bf16), keeps the running
 // maximum / sum, rescales O (at tO) only when the maximum grows by more than 2^8, then normalises, merges and
-// stores. `arrive_p()` tells the MMA issuer that P (and the rescaled O) of this row are in TMEM.
+// stores. `arrive_p()` tells the MMA issuer that P (and the rescaled O) of this row are in TMEM; `arrive_half()` is
+// called when the first 64 keys' P is there (the issuer may start the first half of the PV GEMM under the second
+// half of the exponentials; pass a no-op where that is not used).
 //   tile_row0 = first query row of the tile, row = this thread's query row (both relative to the Q block).
-template <int BN, class ArriveP>
+template <int BN, class ArriveP, class ArriveHalf>
 __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const AbortCtl& ctl, uint64_t* s_full,
-                                                 uint64_t* o_full, ArriveP arrive_p, uint32_t tS, uint32_t tO,
+                                                 uint64_t* o_full, ArriveP arrive_p, ArriveHalf arrive_half, uint32_t tS,
+                                                 uint32_t tO,
                                                  int tile_row0, int row, int nb, int head, int batch, uint32_t tag) {
   const float c = p.scale_log2;
   float m_used = -INFINITY;
@@ -109,6 +112,11 @@ __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const Abort
         pk[i] = pack_bf16(p0, p1);
       }
       tmem_st32(tS + cchunk * 32, pk);
+      if (cchunk == 0 && BN / 64 > 1) {
+        tmem_wait_st();
+        tc_fence_before_sync();
+        arrive_half();
+      }
     }
     float la, lb, lc, ld;
     f2_unpack(ls2[0], la, lb);

@@ -219,8 +219,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
     const uint32_t tS = tmem_base + lane_addr + t * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
     const uint32_t pf0 = mapa_u32(smem_u32(&p_full[t]), 0);
-    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf0] { mbar_arrive_cluster(pf0); }, tS, tO, tile_row0, row,
-                         nblk[t], head, batch, t);
+    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf0] { mbar_arrive_cluster(pf0); }, [] {}, tS, tO, tile_row0,
+                         row, nblk[t], head, batch, t);
   } else {
     setmaxnreg_dec<kFwdRegsLo>();  // warps 2 and 3 only give their registers away
   }
