@@ -31,7 +31,7 @@ struct FwdPairSmem {
   static constexpr int kKOff = kQOff + 2 * kQTile;
   static constexpr int kVOff = kKOff + KST * kKHalf;
   static constexpr int kBarOff = kVOff + VST * kVHalf;
-  static constexpr int kNumBars = 1 + 2 * KST + 2 * VST + 6;
+  static constexpr int kNumBars = 1 + 2 * KST + 2 * VST + 8;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;
 };
@@ -51,10 +51,12 @@ __device__ __forceinline__ void issue_qk_pair(uint32_t d_tmem, uint64_t qdesc, u
 }
 // O[256 x 128] (+)= P[256 x 128] (bf16 in each CTA's TMEM) V_blk[128 x 128]; per CTA V half = [128 keys][64 columns]
 // MN-major (one 64-wide column block), 16 keys = 2048 bytes per K-step.
+// K-steps [K0, K1) of the block's 8: the first half can run as soon as the first 64 keys' P has been stored.
+template <int K0, int K1>
 __device__ __forceinline__ void issue_pv_pair(uint32_t d_tmem, uint32_t p_tmem, uint64_t vdesc, uint32_t idesc,
                                               bool acc, bool leader) {
 #pragma unroll
-  for (int kk = 0; kk < kPairBN / 16; ++kk)
+  for (int kk = K0; kk < K1; ++kk)
     if (leader) umma_ts_pair(d_tmem, p_tmem + kk * 8, desc_advance(vdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
 }
 
@@ -79,6 +81,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
   uint64_t* s_full = v_empty + VST;   // [2] both
   uint64_t* p_full = s_full + 2;      // [2] rank 0 only, 256 arrivals
   uint64_t* o_full = p_full + 2;      // [2] both
+  uint64_t* ph_full = o_full + 2;     // [2] rank 0 only, 256 arrivals: P of the block's first 64 keys is in TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -115,7 +118,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
     mbar_init(q_full, 1);
     for (int i = 0; i < KST; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
     for (int i = 0; i < VST; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 256); mbar_init(&o_full[t], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 256); mbar_init(&o_full[t], 1); mbar_init(&ph_full[t], 256); }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -193,9 +196,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < nblk[t]) {
+            mbar_wait(&ph_full[t], j & 1, ctl, 0x680 + t);
+            tc_fence_after_sync();
+            issue_pv_pair<0, 4>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0, leader);
             mbar_wait(&p_full[t], j & 1, ctl, 0x600 + t);
             tc_fence_after_sync();
-            issue_pv_pair(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, j > 0, leader);
+            issue_pv_pair<4, 8>(tmem_base + 256 + t * 128, tmem_base + t * 128, vd[vs], idesc_pv, true, leader);
             if (j + 1 < nblk[t]) {
               issue_qk_pair<DQK>(tmem_base + t * 128, qd[t], kd[ks], idesc_qk, leader);
               if (leader) umma_commit_pair(&s_full[t]);
@@ -219,8 +225,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
     const uint32_t tS = tmem_base + lane_addr + t * 128;
     const uint32_t tO = tmem_base + lane_addr + 256 + t * 128;
     const uint32_t pf0 = mapa_u32(smem_u32(&p_full[t]), 0);
-    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf0] { mbar_arrive_cluster(pf0); }, [] {}, tS, tO, tile_row0,
-                         row, nblk[t], head, batch, t);
+    const uint32_t ph0 = mapa_u32(smem_u32(&ph_full[t]), 0);
+    fwd_softmax_rows<BN>(p, ctl, &s_full[t], &o_full[t], [pf0] { mbar_arrive_cluster(pf0); },
+                         [ph0] { mbar_arrive_cluster(ph0); }, tS, tO, tile_row0, row, nblk[t], head, batch, t);
   } else {
     setmaxnreg_dec<kFwdRegsLo>();  // warps 2 and 3 only give their registers away
   }
