@@ -38,23 +38,26 @@ constexpr int kRegsLo = 72;
 constexpr int kRegsHi = 208;
 constexpr int kT = 128;             // tile edge (rows of both tiles, head dimension)
 constexpr int kTile = kT * kT * 2;  // bytes of one bf16 tile
-constexpr int kNST = 2;   // stages of each streamed-tile ring that have shared memory of their own
-constexpr int kNSTQ = 3;  // mode kDq: one more stage per ring in the resident tiles' shared memory, which is free once
-                          // they have been copied into TMEM. K_j is read first by S(j) and last by dQ(j), so a stage
-                          // is held for a whole iteration and a two-deep ring leaves the next load (a TMA round trip
-                          // of ~2000 cycles) no time before S(j+1) wants it.
+// Ring depths. X1 (Q_i / K_j) is read first by the score GEMM of an iteration and last by its final GEMM, so a stage is
+// held for a whole iteration, and a two-deep ring leaves the next load (a TMA round trip of ~2000 cycles) no time before
+// the next-but-one score GEMM wants it: three stages. X2 (dO_i / V_j) is released early: two stages, plus in mode kDq a
+// third one in the resident dO tile's shared memory, which is free once the resident tiles have been copied into TMEM
+// (a fourth K_j stage in the resident Q tile's memory measured slower). With two stages for Q_i the dK/dV pass took
+// 1.08 ms on 32 heads x 8192^2 causal; with three, 0.87 ms.
+constexpr int kNS1 = 3;
+constexpr int kNS2 = 2;
 constexpr int kMaxST = 3;
 
 struct Smem {
   static constexpr int kR1Off = 0;
   static constexpr int kR2Off = kR1Off + kTile;
   static constexpr int kX1Off = kR2Off + kTile;
-  static constexpr int kX2Off = kX1Off + kNST * kTile;
-  static constexpr int kStatOff = kX2Off + kNST * kTile;  // [kNST][2][128] floats
-  static constexpr int kBarOff = kStatOff + kNST * 2 * kT * 4;
-  static constexpr int kNumBars = 1 + 4 * kMaxST + 6;
+  static constexpr int kX2Off = kX1Off + kNS1 * kTile;
+  static constexpr int kStatOff = kX2Off + kNS2 * kTile;  // [2][2][128] floats: a two-deep ring of its own
+  static constexpr int kBarOff = kStatOff + 2 * 2 * kT * 4;
+  static constexpr int kNumBars = 1 + 4 * kMaxST + 6 + 4;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
-  static constexpr int kAlloc = kTotal + 1024;
+  static constexpr int kAlloc = kTotal;  // no slack: the kernel checks that the dynamic window starts 1024-aligned
 };
 static_assert(Smem::kAlloc <= 232448, "shared memory budget");
 
@@ -109,16 +112,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
                        const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
                        const BwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sR1 = smem + Smem::kR1Off;
   uint8_t* sR2 = smem + Smem::kR2Off;
   uint8_t* sX1 = smem + Smem::kX1Off;
   uint8_t* sX2 = smem + Smem::kX2Off;
   float* sStat = reinterpret_cast<float*>(smem + Smem::kStatOff);
-  constexpr int NS = (MODE == kDq) ? kNSTQ : kNST;  // ring depth of this mode
-  auto x1_stage = [&](int st) { return st < kNST ? sX1 + st * kTile : sR1; };
-  auto x2_stage = [&](int st) { return st < kNST ? sX2 + st * kTile : sR2; };
+  constexpr int NS1 = kNS1;
+  constexpr int NS2 = (MODE == kDq) ? kNS2 + 1 : kNS2;
+  auto x1_stage = [&](int st) { return sX1 + st * kTile; };
+  auto x2_stage = [&](int st) { return st < kNS2 ? sX2 + st * kTile : sR2; };
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBarOff);
   uint64_t* res_full = bars;
   // The two streamed tiles have separate rings: X2 (dO_i / V_j) is last used earlier than X1 (Q_i / K_j), so
@@ -133,6 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* ds_full = p_full + 1;   // dS is in TMEM
   uint64_t* acc_full = ds_full + 1;
   uint64_t* rt_full = acc_full + 1;  // kDq: resident tiles are in TMEM
+  uint64_t* st_full = rt_full + 1;   // kDkDv: statistics of the streamed queries (two stages)
+  uint64_t* st_empty = st_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -164,7 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) ? 1u : 0u;
     mbar_init(res_full, 1);
     for (int i = 0; i < kMaxST; ++i) {
-      mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
+      mbar_init(&x_full[i], 1);
       mbar_init(&x_empty[i], 1);
       mbar_init(&x2_full[i], 1);
       mbar_init(&x2_empty[i], 1);
@@ -175,6 +180,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(ds_full, 256);
     mbar_init(acc_full, 1);
     mbar_init(rt_full, 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&st_full[i], 1);
+      mbar_init(&st_empty[i], 256);
+    }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -185,6 +194,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled tiles need a 1024-byte aligned window
+    if (threadIdx.x == 0) report_error(ctl, kErrSmemAlign, smem_u32(smem));
+    n_it = 0;
+  }
   if (*abort_flag != 0u) n_it = 0;
 
   const int r1_head = (MODE == kDkDv) ? kv_head : head;  // head index of the resident tensors
@@ -225,30 +238,32 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       };
       auto step = [&](int k, float (&rl)[4], float (&rd)[4]) {
-        const int s = k % NS;
+        const int s1 = k % NS1, s2 = k % NS2;
         const int x0 = (it_begin + k) * kT;
         if (lane == 0) {
-          if (MODE == kDq && k == kNST) mbar_wait(rt_full, 0, ctl, 0x1F0);  // the resident tiles' memory is free now
-          mbar_wait(&x_empty[s], ((k / NS) & 1) ^ 1, ctl, 0x100 + s);
-          mbar_arrive_expect_tx(&x_full[s], kTile);
+          if (MODE == kDq && k == kNS2) mbar_wait(rt_full, 0, ctl, 0x1F0);  // the resident tiles' memory is free now
+          mbar_wait(&x_empty[s1], ((k / NS1) & 1) ^ 1, ctl, 0x100 + s1);
+          mbar_arrive_expect_tx(&x_full[s1], kTile);
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub)
-            tma_load_4d(x1_stage(s) + sub * (kT * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
-          mbar_wait(&x2_empty[s], ((k / NS) & 1) ^ 1, ctl, 0x180 + s);
-          mbar_arrive_expect_tx(&x2_full[s], kTile);
+            tma_load_4d(x1_stage(s1) + sub * (kT * 128), &tm_x1, &x_full[s1], sub * 64, x_head, x0, batch);
+          mbar_wait(&x2_empty[s2], ((k / NS2) & 1) ^ 1, ctl, 0x180 + s2);
+          mbar_arrive_expect_tx(&x2_full[s2], kTile);
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub)
-            tma_load_4d(x2_stage(s) + sub * (kT * 128), &tm_x2, &x2_full[s], sub * 64, x_head, x0, batch);
+            tma_load_4d(x2_stage(s2) + sub * (kT * 128), &tm_x2, &x2_full[s2], sub * 64, x_head, x0, batch);
         }
-        __syncwarp();  // the stage is free (lane 0 saw x_empty) before anyone writes its statistics
         if constexpr (MODE == kDkDv) {
+          const int ss = k & 1;
+          if (lane == 0) mbar_wait(&st_empty[ss], ((k >> 1) & 1) ^ 1, ctl, 0x1C0 + ss);
+          __syncwarp();  // the statistics stage is free before anyone writes it
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            sStat[(s * 2 + 0) * kT + j * 32 + lane] = (rl[j] == -INFINITY) ? -INFINITY : -rl[j];
-            sStat[(s * 2 + 1) * kT + j * 32 + lane] = -rd[j];
+            sStat[(ss * 2 + 0) * kT + j * 32 + lane] = (rl[j] == -INFINITY) ? -INFINITY : -rl[j];
+            sStat[(ss * 2 + 1) * kT + j * 32 + lane] = -rd[j];
           }
           __syncwarp();
-          if (lane == 0) mbar_arrive(&x_full[s]);
+          if (lane == 0) mbar_arrive(&st_full[ss]);
           load_stats(k + 2, rl, rd);  // consumed two steps from now
         }
       };
@@ -268,16 +283,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       constexpr uint32_t idesc_kk = make_idesc_bf16(kT, kT, false, false);  // both operands K-major
       constexpr uint32_t idesc_mn = make_idesc_bf16(kT, kT, false, true);   // B operand MN-major
       const uint64_t r1d = make_smem_desc(smem_u32(sR1), 16, 1024), r2d = make_smem_desc(smem_u32(sR2), 16, 1024);
-      uint64_t x1k[NS], x2k[NS], x1m[NS], x2m[NS];
+      uint64_t x1k[NS1], x2k[NS2], x1m[NS1], x2m[NS2];
 #pragma unroll
-      for (int s = 0; s < NS; ++s) {
+      for (int s = 0; s < NS1; ++s) {
         x1k[s] = make_smem_desc(smem_u32(x1_stage(s)), 16, 1024);
-        x2k[s] = make_smem_desc(smem_u32(x2_stage(s)), 16, 1024);
         x1m[s] = make_smem_desc(smem_u32(x1_stage(s)), kT * 128, 1024);
+      }
+#pragma unroll
+      for (int s = 0; s < NS2; ++s) {
+        x2k[s] = make_smem_desc(smem_u32(x2_stage(s)), 16, 1024);
         x2m[s] = make_smem_desc(smem_u32(x2_stage(s)), kT * 128, 1024);
       }
       // register selects instead of runtime-indexed arrays (which would live in local memory)
-      auto pick = [](const uint64_t (&d)[NS], int st) { return st == 0 ? d[0] : (st == 1 || NS == 2) ? d[1] : d[NS - 1]; };
+      auto pick1 = [](const uint64_t (&d)[NS1], int st) { return st == 0 ? d[0] : st == 1 ? d[1] : d[2]; };
+      auto pick2 = [](const uint64_t (&d)[NS2], int st) { return st == 0 ? d[0] : (st == 1 || NS2 == 2) ? d[1] : d[NS2 - 1]; };
       const uint32_t t1 = tmem_base + kColT1, t2 = tmem_base + kColT2;
       if constexpr (MODE == kDq) {
         mbar_wait(rt_full, 0, ctl, 0x210);
@@ -305,48 +324,50 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (leader) umma_commit(&x2_empty[0]);  // V_0 is only read by dP(0)
       }
       for (int k = 0; k < n_it; ++k) {
-        const int s = k % NS, sn = (k + 1) % NS;                       // stages of iterations k and k + 1
-        const uint32_t ph_n = static_cast<uint32_t>((k + 1) / NS) & 1u;  // phase of stage sn's "full" barrier
+        const int s1 = k % NS1, sn1 = (k + 1) % NS1;  // stages of iterations k and k + 1 in either ring
+        const int s2 = k % NS2, sn2 = (k + 1) % NS2;
+        const uint32_t ph1 = static_cast<uint32_t>((k + 1) / NS1) & 1u;  // phases of the "full" barriers of sn1, sn2
+        const uint32_t ph2 = static_cast<uint32_t>((k + 1) / NS2) & 1u;
         const bool more = k + 1 < n_it;
         if constexpr (MODE == kDkDv) {
           mbar_wait(p_full, k & 1, ctl, 0x400);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t1, pick(x2m, s), idesc_mn, k > 0, leader);  // dV += P^T dO_i
-          if (leader) umma_commit(&x2_empty[s]);  // last use of dO_i
+          gemm_ts(tmem_base + kColAcc, t1, pick2(x2m, s2), idesc_mn, k > 0, leader);  // dV += P^T dO_i
+          if (leader) umma_commit(&x2_empty[s2]);  // last use of dO_i
           if (more) {
-            mbar_wait(&x_full[sn], ph_n, ctl, 0x300 + sn);
+            mbar_wait(&x_full[sn1], ph1, ctl, 0x300 + sn1);
             tc_fence_after_sync();
-            gemm_t1(pick(x1k, sn));  // S^T(k+1)
+            gemm_t1(pick1(x1k, sn1));  // S^T(k+1)
             if (leader) umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc2, t2, pick(x1m, s), idesc_mn, k > 0, leader);  // dK += dS^T Q_i
-          if (leader) umma_commit(&x_empty[s]);
+          gemm_ts(tmem_base + kColAcc2, t2, pick1(x1m, s1), idesc_mn, k > 0, leader);  // dK += dS^T Q_i
+          if (leader) umma_commit(&x_empty[s1]);
           if (more) {
-            mbar_wait(&x2_full[sn], ph_n, ctl, 0x380 + sn);
+            mbar_wait(&x2_full[sn2], ph2, ctl, 0x380 + sn2);
             tc_fence_after_sync();
-            gemm_t2(pick(x2k, sn));  // dP^T(k+1)
+            gemm_t2(pick2(x2k, sn2));  // dP^T(k+1)
             if (leader) umma_commit(t2_full);
           }
         } else {
           if (more) {
-            mbar_wait(&x_full[sn], ph_n, ctl, 0x300 + sn);
+            mbar_wait(&x_full[sn1], ph1, ctl, 0x300 + sn1);
             mbar_wait(p_full, k & 1, ctl, 0x400);  // T1 of iteration k has been read
             tc_fence_after_sync();
-            gemm_t1(pick(x1k, sn));  // S(k+1)
+            gemm_t1(pick1(x1k, sn1));  // S(k+1)
             if (leader) umma_commit(t1_full);
           }
           mbar_wait(ds_full, k & 1, ctl, 0x500);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t2, pick(x1m, s), idesc_mn, k > 0, leader);  // dQ += dS K_j
-          if (leader) umma_commit(&x_empty[s]);
+          gemm_ts(tmem_base + kColAcc, t2, pick1(x1m, s1), idesc_mn, k > 0, leader);  // dQ += dS K_j
+          if (leader) umma_commit(&x_empty[s1]);
           if (more) {
-            mbar_wait(&x2_full[sn], ph_n, ctl, 0x380 + sn);
+            mbar_wait(&x2_full[sn2], ph2, ctl, 0x380 + sn2);
             tc_fence_after_sync();
-            gemm_t2(pick(x2k, sn));  // dP(k+1)
+            gemm_t2(pick2(x2k, sn2));  // dP(k+1)
             if (leader) umma_commit(t2_full);
-            if (leader) umma_commit(&x2_empty[sn]);  // V_j is only read by dP
+            if (leader) umma_commit(&x2_empty[sn2]);  // V_j is only read by dP
           }
         }
       }
@@ -382,9 +403,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     for (int k = 0; k < n_it; ++k) {
-      const int s = k % kNST;  // statistics stage (mode kDkDv, two-deep ring)
+      const int s = k & 1;  // statistics stage (mode kDkDv, two-deep ring)
       const int x0 = (it_begin + k) * kT + h * 64;  // global position of this thread's first column
-      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k / kNST) & 1, ctl, 0x600 + s);
+      if constexpr (MODE == kDkDv) mbar_wait(&st_full[s], (k >> 1) & 1, ctl, 0x600 + s);
       const ulonglong2* st_l = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 0) * kT + h * 64);
       const ulonglong2* st_d = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 1) * kT + h * 64);
       // key n visible to query m iff n <= m + off
@@ -484,6 +505,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           da[j >> 1] = pack_bf16(g0, g1);
         }
       }
+      if constexpr (MODE == kDkDv) mbar_arrive(&st_empty[s]);  // last read of this iteration's statistics
       tmem_st32(t2, da);
       tmem_wait_st();
       tc_fence_before_sync();

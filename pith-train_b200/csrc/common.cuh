@@ -20,6 +20,7 @@ namespace pith {
 enum : uint32_t {
   kErrWaitTimeout = 1u,   // an mbarrier wait ran out of cycles
   kErrTmemAlloc = 2u,     // TMEM allocation returned an unexpected base
+  kErrSmemAlign = 4u,     // the dynamic shared-memory window does not start on a 1024-byte boundary (3 = peer wait)
 };
 
 struct AbortCtl {

@@ -84,6 +84,8 @@ const char* pith_status_string(uint32_t status) {
     snprintf(buf, sizeof buf, "wait for a ring neighbour timed out (sequence number 0x%06x)", detail);
   else if (code == pith::kErrTmemAlloc)
     snprintf(buf, sizeof buf, "unexpected TMEM allocation (0x%06x)", detail);
+  else if (code == pith::kErrSmemAlign)
+    snprintf(buf, sizeof buf, "shared-memory window not 1024-byte aligned (offset 0x%06x)", detail);
   else
     snprintf(buf, sizeof buf, "unknown device status 0x%08x", status);
   return buf;
