@@ -53,10 +53,15 @@ struct BwdCfg {
   static constexpr int kX2Off = kX1Off + NST * kX1;
   static constexpr int kStatOff = kX2Off + NST * kX2;        // [NST][2][64] floats
   static constexpr int kBarOff = kStatOff + NST * 2 * kStr * 4;
-  static constexpr int kNumBars = 1 + 2 * NST + 2 + 2 + 1;
+  static constexpr int kNumBars = 1 + 2 * NST + 2 + 2 + 1 + 2;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
   static constexpr int kAlloc = kTotal + 1024;
-  static constexpr int kAccCol = NBUF * 128;  // first accumulator column
+  // With a single buffer (the 192 + 128 accumulator columns of mode kDkDv leave 192), the packed operands A1 / A2 get
+  // 64 columns of their own behind it: the next iteration's T GEMMs may overwrite the buffer as soon as the compute
+  // group has loaded it, instead of after the accumulating GEMMs have read A1 / A2 out of it.
+  static constexpr bool kSplitA = NBUF == 1;
+  static constexpr int kACol = 128;
+  static constexpr int kAccCol = kSplitA ? 192 : NBUF * 128;  // first accumulator column
 };
 
 template <int DQK, int MODE>
@@ -80,6 +85,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   uint64_t* t_full = x_empty + NST;  // [2], by compute group
   uint64_t* a_full = t_full + 2;     // [2]
   uint64_t* acc_full = a_full + 2;
+  uint64_t* t_read = acc_full + 1;  // kSplitA: the buffer has been loaded into registers
+  uint64_t* a_free = t_read + 1;    // kSplitA: the accumulating GEMMs have read A1 / A2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -120,6 +127,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       mbar_init(&a_full[i], 128);
     }
     mbar_init(acc_full, 1);
+    mbar_init(t_read, 128);
+    mbar_init(a_free, 1);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -225,10 +234,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       issue_t(0);
       for (int k = 0; k < n_it; ++k) {
         if (NBUF == 2 && k + 1 < n_it) issue_t(k + 1);
+        if (C::kSplitA && k + 1 < n_it) {
+          mbar_wait(t_read, k & 1, ctl, 0x480);
+          tc_fence_after_sync();
+          issue_t(k + 1);
+        }
         const int s = k % NST, b = k % NBUF;
         mbar_wait(&a_full[k & 1], (k >> 1) & 1, ctl, 0x400 + (k & 1));
         tc_fence_after_sync();
-        const uint32_t a1 = tmem_base + b * 128, a2 = a1 + 64;
+        const uint32_t a1 = C::kSplitA ? tmem_base + C::kACol : tmem_base + b * 128, a2 = a1 + (C::kSplitA ? 32 : 64);
         const uint32_t acc = k > 0 ? 1u : 0u;
         const uint64_t x1s = desc_advance(x1m, s * C::kX1), x2s = desc_advance(x2m, s * C::kX2);
         if constexpr (MODE == kDkDv) {
@@ -248,7 +262,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
               umma_ts(tmem_base + C::kAccCol, a2 + kk * 8, desc_advance(x1s, kk * 2048), idesc_dqk, acc | (kk > 0 ? 1u : 0u));
         }
         if (leader) umma_commit(&x_empty[s]);
-        if (NBUF == 1 && k + 1 < n_it) issue_t(k + 1);
+        if (C::kSplitA && leader) umma_commit(a_free);
       }
       if (leader) umma_commit(acc_full);
     }
@@ -282,6 +296,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tmem_ld32(t2, s2);
       tmem_ld32(t2 + 32, s2 + 32);
       tmem_wait_ld();
+      if constexpr (C::kSplitA) {
+        tc_fence_before_sync();
+        mbar_arrive(t_read);
+      }
       // key n visible to query m iff n <= m + off
       bool need_mask;
       int lim;  // kDkDv: first visible column (query) index; kDq: last visible column (key) index
@@ -323,8 +341,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         pa[i >> 1] = pack_bf16(p0, p1);
         da[i >> 1] = pack_bf16(g0, g1);
       }
-      if constexpr (MODE == kDkDv) tmem_st32(t1, pa);
-      tmem_st32(t2, da);
+      if constexpr (C::kSplitA) {
+        if (k > 0) {
+          mbar_wait(a_free, (k - 1) & 1, ctl, 0x680);
+          tc_fence_after_sync();
+        }
+        tmem_st32(tmem_base + lane_addr + C::kACol, pa);
+        tmem_st32(tmem_base + lane_addr + C::kACol + 32, da);
+      } else {
+        if constexpr (MODE == kDkDv) tmem_st32(t1, pa);
+        tmem_st32(t2, da);
+      }
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&a_full[w]);
