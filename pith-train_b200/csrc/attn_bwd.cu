@@ -18,12 +18,17 @@
 // atomics, so ring steps and the query heads of a GQA group round to bf16 only once.
 //
 // Warp roles (384 threads): warp 0 TMA producer (+ the per-query statistics of the streamed tile
-// in mode kDkDv), warp 1 MMA issuer, warps 4..7 / 8..11 two compute groups that alternate
-// iterations (and TMEM buffers when two fit), so the tensor core works on one iteration while
-// the other is in the exponentials.
+// in mode kDkDv, loaded two iterations ahead), warp 1 MMA issuer, warps 4..7 / 8..11 two compute groups.
+//   mode kDq: two TMEM buffers; the groups alternate iterations, so the tensor core works on one iteration
+//     while the other is in the exponentials.
+//   mode kDkDv: the 192 + 128 accumulator columns leave room for one buffer, so both groups work on every
+//     tile (32 of its 64 columns each), the packed operands A1 / A2 get 64 columns of their own, and the next
+//     tile's T GEMMs are issued as soon as the buffer has been loaded into registers.
+// The two streamed tensors have separate TMA rings (X1: four stages, X2: three).
 //
-// TMEM columns: buffer b at [128 b, 128 b + 128): T1 in the first 64 columns, T2 in the last 64;
-// A1 / A2 (packed bf16) overlay the first 32 columns of T1 / T2. Accumulators follow the buffers.
+// TMEM columns, mode kDq: buffer b at [128 b, 128 b + 128): T1 in the first 64 columns, T2 in the last 64,
+// A2 (packed bf16) overlays the first 32 columns of T2; dQ accumulator at [256, 448).
+// Mode kDkDv: T1 [0, 64), T2 [64, 128), A1 [128, 160), A2 [160, 192), dV [192, 320), dK [320, 512).
 #include "../../include/pith_b200.h"
 #include "common.cuh"
 #include <mutex>
@@ -39,10 +44,14 @@ constexpr int kBwdRegsHi = 208;  // compute warpgroups (128 * 72 + 256 * 208 <= 
 constexpr int kRes = 128;  // rows of the resident tile (= TMEM lanes)
 constexpr int kStr = 64;   // rows of a streamed tile (= columns of T1 / T2)
 
+
 template <int DQK, int MODE>
 struct BwdCfg {
   static constexpr int NBUF = (MODE == kDkDv && DQK == 192) ? 1 : 2;
-  static constexpr int NST = (DQK == 128) ? 4 : 3;
+  // Ring depths: X1 (Q_i / K_j) is read by the first GEMM of an iteration and by its last, X2 (dO_i / V_j) is released
+  // earlier; a reload is a TMA round trip of ~2000 cycles, more than an iteration, so X1 gets the deeper ring.
+  static constexpr int NS1 = 4;
+  static constexpr int NS2 = 3;
   static constexpr int kR1 = kRes * DQK * 2;
   static constexpr int kR2 = kRes * 128 * 2;
   static constexpr int kX1 = kStr * DQK * 2;
@@ -50,12 +59,13 @@ struct BwdCfg {
   static constexpr int kR1Off = 0;
   static constexpr int kR2Off = kR1Off + kR1;
   static constexpr int kX1Off = kR2Off + kR2;
-  static constexpr int kX2Off = kX1Off + NST * kX1;
-  static constexpr int kStatOff = kX2Off + NST * kX2;        // [NST][2][64] floats
-  static constexpr int kBarOff = kStatOff + NST * 2 * kStr * 4;
-  static constexpr int kNumBars = 1 + 2 * NST + 2 + 2 + 1 + 2;
+  static constexpr int kX2Off = kX1Off + NS1 * kX1;
+  static constexpr int kStatOff = kX2Off + NS2 * kX2;        // [NS1][2][64] floats
+  static constexpr int kBarOff = kStatOff + NS1 * 2 * kStr * 4;
+  static constexpr int kNumBars = 1 + 2 * NS1 + 2 * NS2 + 2 + 2 + 1 + 2;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
-  static constexpr int kAlloc = kTotal + 1024;
+  static constexpr int kAlloc = kTotal;  // no slack: the kernel checks that the dynamic window starts 1024-aligned
+  static_assert(kAlloc <= 232448, "shared memory budget");
   // With a single buffer (the 192 + 128 accumulator columns of mode kDkDv leave 192), the packed operands A1 / A2 get
   // 64 columns of their own behind it: the next iteration's T GEMMs may overwrite the buffer as soon as the compute
   // group has loaded it, instead of after the accumulating GEMMs have read A1 / A2 out of it.
@@ -70,9 +80,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     const __grid_constant__ CUtensorMap tm_x1, const __grid_constant__ CUtensorMap tm_x2,
                     const BwdParams p) {
   using C = BwdCfg<DQK, MODE>;
-  constexpr int NBUF = C::NBUF, NST = C::NST;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int NBUF = C::NBUF, NS1 = C::NS1, NS2 = C::NS2;
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sR1 = smem + C::kR1Off;
   uint8_t* sR2 = smem + C::kR2Off;
   uint8_t* sX1 = smem + C::kX1Off;
@@ -80,9 +89,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   float* sStat = reinterpret_cast<float*>(smem + C::kStatOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
   uint64_t* res_full = bars;
-  uint64_t* x_full = bars + 1;
-  uint64_t* x_empty = x_full + NST;
-  uint64_t* t_full = x_empty + NST;  // [2], by compute group
+  uint64_t* x_full = bars + 1;        // X1 (+ statistics in kDkDv)
+  uint64_t* x_empty = x_full + NS1;
+  uint64_t* x2_full = x_empty + NS1;  // X2
+  uint64_t* x2_empty = x2_full + NS2;
+  uint64_t* t_full = x2_empty + NS2;  // [2], by compute group
   uint64_t* a_full = t_full + 2;     // [2]
   uint64_t* acc_full = a_full + 2;
   uint64_t* t_read = acc_full + 1;  // kSplitA: the buffer has been loaded into registers
@@ -94,17 +105,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   const int lane = threadIdx.x & 31;
   const AbortCtl ctl{p.status, abort_flag};
 
-  const int head = blockIdx.y;
+  int tile_i, head;
+  launch_order(blockIdx.x, gridDim.x, p.causal != 0, tile_i, head);
   const int batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   // Tile of the resident operand and the range of streamed tiles it meets.
   int r0, it_begin, it_end;
   if constexpr (MODE == kDkDv) {
-    r0 = blockIdx.x * kRes;  // first key; small r0 = most work, launched first
+    r0 = tile_i * kRes;  // first key; small r0 = most work, launched first
     it_begin = p.causal ? max(0, r0 - p.causal_off) / kStr : 0;
     it_end = (p.Sq + kStr - 1) / kStr;
   } else {
-    r0 = (gridDim.x - 1 - blockIdx.x) * kRes;  // first query; late queries first
+    r0 = (gridDim.x - 1 - tile_i) * kRes;  // first query; late queries first
     it_begin = 0;
     it_end = (p.Sk + kStr - 1) / kStr;
     if (p.causal) {
@@ -118,16 +130,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     // a launch that finds an error already recorded (by an earlier CTA or launch) does no work
     *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile uint32_t*>(p.status) != 0u) ? 1u : 0u;
     mbar_init(res_full, 1);
-    for (int i = 0; i < NST; ++i) {
+    for (int i = 0; i < NS1; ++i) {
       mbar_init(&x_full[i], MODE == kDkDv ? 2 : 1);
       mbar_init(&x_empty[i], 1);
     }
+    for (int i = 0; i < NS2; ++i) {
+      mbar_init(&x2_full[i], 1);
+      mbar_init(&x2_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&t_full[i], 1);
-      mbar_init(&a_full[i], 128);
+      mbar_init(&a_full[i], C::kSplitA ? 256 : 128);
     }
     mbar_init(acc_full, 1);
-    mbar_init(t_read, 128);
+    mbar_init(t_read, 256);
     mbar_init(a_free, 1);
     mbar_fence_init();
   }
@@ -139,6 +155,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled tiles need a 1024-byte aligned window
+    if (threadIdx.x == 0) report_error(ctl, kErrSmemAlign, smem_u32(smem));
+    n_it = 0;
+  }
   if (*abort_flag != 0u) n_it = 0;
 
   const int r1_head = (MODE == kDkDv) ? kv_head : head;  // head index of the resident tensors
@@ -161,37 +181,59 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         for (int sub = 0; sub < 2; ++sub)
           tma_load_4d(sR2 + sub * (kRes * 128), &tm_r2, res_full, sub * 64, r1_head, r0, batch);
       }
-      for (int k = 0; k < n_it; ++k) {
-        const int s = k % NST;
+      // Statistics of the 64 streamed queries (kDkDv): raw lse / delta of iteration k are loaded two iterations ahead
+      // into registers (a plain global load takes thousands of cycles next to the TMA traffic, and the stage's "full"
+      // barrier waits for them) and written to the stage as -lse (+inf -> -inf where the row does not exist or saw
+      // no key) and -delta.
+      auto load_stats = [&](int k, float (&rl)[2], float (&rd)[2]) {
+        if constexpr (MODE == kDkDv) {
+          const int x0 = (it_begin + k) * kStr;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int m = x0 + j * 32 + lane;
+            rl[j] = INFINITY;
+            rd[j] = 0.f;
+            if (k < n_it && m < p.Sq) {
+              rl[j] = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
+              rd[j] = p.delta[batch * p.dls[0] + head * p.dls[1] + m];
+              if (rl[j] == -INFINITY) rl[j] = INFINITY;
+            }
+          }
+        }
+      };
+      auto step = [&](int k, float (&rl)[2], float (&rd)[2]) {
+        const int s = k % NS1, s2 = k % NS2;
         const int x0 = (it_begin + k) * kStr;
-        if (lane == 0) mbar_wait(&x_empty[s], ((k / NST) & 1) ^ 1, ctl, 0x100 + s);
-        __syncwarp();
         if (lane == 0) {
-          mbar_arrive_expect_tx(&x_full[s], C::kX1 + C::kX2);
+          mbar_wait(&x_empty[s], ((k / NS1) & 1) ^ 1, ctl, 0x100 + s);
+          mbar_arrive_expect_tx(&x_full[s], C::kX1);
 #pragma unroll
           for (int sub = 0; sub < DQK / 64; ++sub)
             tma_load_4d(sX1 + s * C::kX1 + sub * (kStr * 128), &tm_x1, &x_full[s], sub * 64, x_head, x0, batch);
+          mbar_wait(&x2_empty[s2], ((k / NS2) & 1) ^ 1, ctl, 0x180 + s2);
+          mbar_arrive_expect_tx(&x2_full[s2], C::kX2);
 #pragma unroll
           for (int sub = 0; sub < 2; ++sub)
-            tma_load_4d(sX2 + s * C::kX2 + sub * (kStr * 128), &tm_x2, &x_full[s], sub * 64, x_head, x0, batch);
+            tma_load_4d(sX2 + s2 * C::kX2 + sub * (kStr * 128), &tm_x2, &x2_full[s2], sub * 64, x_head, x0, batch);
         }
+        __syncwarp();  // the X1 stage is free (lane 0 saw x_empty) before anyone writes its statistics
         if constexpr (MODE == kDkDv) {
-          // statistics of the 64 streamed queries: -lse (-inf where the row does not exist or saw no key), -delta
 #pragma unroll
-          for (int r = lane; r < kStr; r += 32) {
-            const int m = x0 + r;
-            float l = INFINITY, d = 0.f;
-            if (m < p.Sq) {
-              l = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
-              d = p.delta[batch * p.dls[0] + head * p.dls[1] + m];
-              if (l == -INFINITY) l = INFINITY;
-            }
-            sStat[(s * 2 + 0) * kStr + r] = -l;  // stored negated: the consumers only ever add them
-            sStat[(s * 2 + 1) * kStr + r] = -d;
+          for (int j = 0; j < 2; ++j) {
+            sStat[(s * 2 + 0) * kStr + j * 32 + lane] = -rl[j];  // stored negated: the consumers only ever add them
+            sStat[(s * 2 + 1) * kStr + j * 32 + lane] = -rd[j];
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&x_full[s]);
+          load_stats(k + 2, rl, rd);  // consumed two steps from now
         }
+      };
+      float la[2], da_[2], lb[2], db[2];
+      load_stats(0, la, da_);
+      load_stats(1, lb, db);
+      for (int k = 0; k < n_it; k += 2) {
+        step(k, la, da_);
+        if (k + 1 < n_it) step(k + 1, lb, db);
       }
     }
   } else if (warp == 1) {
@@ -210,11 +252,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       const uint64_t x2m = make_smem_desc(smem_u32(sX2), kStr * 128, 1024);
       mbar_wait(res_full, 0, ctl, 0x200);
       auto issue_t = [&](int k) {
-        const int s = k % NST, b = k % NBUF;
-        mbar_wait(&x_full[s], (k / NST) & 1, ctl, 0x300 + s);
+        const int s = k % NS1, s2 = k % NS2, b = k % NBUF;
+        mbar_wait(&x_full[s], (k / NS1) & 1, ctl, 0x300 + s);
         tc_fence_after_sync();
         const uint32_t t1 = tmem_base + b * 128, t2 = t1 + 64;
-        const uint64_t x1s = desc_advance(x1k, s * C::kX1), x2s = desc_advance(x2k, s * C::kX2);
+        const uint64_t x1s = desc_advance(x1k, s * C::kX1), x2s = desc_advance(x2k, s2 * C::kX2);
 #pragma unroll
         for (int kk = 0; kk < DQK / 16; ++kk) {
           const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
@@ -222,6 +264,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             umma_ss(t1, desc_advance(r1d, sub * (kRes * 128) + off), desc_advance(x1s, sub * (kStr * 128) + off), idesc_t,
                     kk > 0 ? 1u : 0u);
         }
+        mbar_wait(&x2_full[s2], (k / NS2) & 1, ctl, 0x380 + s2);
+        tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           const uint32_t sub = kk >> 2, off = (kk & 3) * 32;
@@ -229,27 +273,23 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             umma_ss(t2, desc_advance(r2d, sub * (kRes * 128) + off), desc_advance(x2s, sub * (kStr * 128) + off), idesc_t,
                     kk > 0 ? 1u : 0u);
         }
-        if (leader) umma_commit(&t_full[k & 1]);
+        if (leader) umma_commit(&t_full[C::kSplitA ? 0 : (k & 1)]);
+        if (MODE == kDq && leader) umma_commit(&x2_empty[s2]);  // V_j is only read by dP
       };
-      issue_t(0);
-      for (int k = 0; k < n_it; ++k) {
-        if (NBUF == 2 && k + 1 < n_it) issue_t(k + 1);
-        if (C::kSplitA && k + 1 < n_it) {
-          mbar_wait(t_read, k & 1, ctl, 0x480);
-          tc_fence_after_sync();
-          issue_t(k + 1);
-        }
-        const int s = k % NST, b = k % NBUF;
-        mbar_wait(&a_full[k & 1], (k >> 1) & 1, ctl, 0x400 + (k & 1));
+      auto issue_acc = [&](int k) {
+        const int s = k % NS1, s2 = k % NS2, b = k % NBUF;
+        if constexpr (C::kSplitA) mbar_wait(&a_full[0], k & 1, ctl, 0x400);
+        else mbar_wait(&a_full[k & 1], (k >> 1) & 1, ctl, 0x400 + (k & 1));
         tc_fence_after_sync();
         const uint32_t a1 = C::kSplitA ? tmem_base + C::kACol : tmem_base + b * 128, a2 = a1 + (C::kSplitA ? 32 : 64);
         const uint32_t acc = k > 0 ? 1u : 0u;
-        const uint64_t x1s = desc_advance(x1m, s * C::kX1), x2s = desc_advance(x2m, s * C::kX2);
+        const uint64_t x1s = desc_advance(x1m, s * C::kX1), x2s = desc_advance(x2m, s2 * C::kX2);
         if constexpr (MODE == kDkDv) {
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dV += P^T dO_i
             if (leader)
               umma_ts(tmem_base + C::kAccCol, a1 + kk * 8, desc_advance(x2s, kk * 2048), idesc_dv, acc | (kk > 0 ? 1u : 0u));
+          if (leader) umma_commit(&x2_empty[s2]);  // last use of dO_i
 #pragma unroll
           for (int kk = 0; kk < kStr / 16; ++kk)  // dK += dS^T Q_i
             if (leader)
@@ -263,6 +303,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
         if (leader) umma_commit(&x_empty[s]);
         if (C::kSplitA && leader) umma_commit(a_free);
+      };
+      issue_t(0);
+      if constexpr (C::kSplitA) {
+        for (int k = 0; k < n_it; ++k) {
+          if (k + 1 < n_it) {
+            mbar_wait(t_read, k & 1, ctl, 0x480);
+            tc_fence_after_sync();
+            issue_t(k + 1);
+          }
+          issue_acc(k);
+        }
+      } else {
+        for (int k = 0; k < n_it; ++k) {
+          if (k + 1 < n_it) issue_t(k + 1);
+          issue_acc(k);
+        }
       }
       if (leader) umma_commit(acc_full);
     }
@@ -283,10 +339,59 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       }
     }
     const uint64_t my_nl2 = f2_pack(-my_lse, -my_lse), my_nd2 = f2_pack(-my_delta, -my_delta);
+    if constexpr (C::kSplitA) {
+      // Both groups work on every tile, 32 of its 64 columns each: half the latency from the score GEMMs to the
+      // accumulating GEMMs, which is what the single buffer makes the iteration wait for.
+      const uint64_t c2 = f2_pack(c, c);
+      const uint32_t t1 = tmem_base + lane_addr + w * 32, t2 = t1 + 64;
+      const uint32_t ta = tmem_base + lane_addr + C::kACol + w * 16;
+      for (int k = 0; k < n_it; ++k) {
+        const int s = k % NS1;
+        const int x0 = (it_begin + k) * kStr + w * 32;  // global position of this thread's first column
+        mbar_wait(&x_full[s], (k / NS1) & 1, ctl, 0x500 + s);
+        mbar_wait(&t_full[0], k & 1, ctl, 0x600);
+        tc_fence_after_sync();
+        uint32_t s1[32], s2[32];
+        tmem_ld32(t1, s1);
+        tmem_ld32(t2, s2);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(t_read);
+        const bool need_mask = p.causal && (r0 + kRes - 1 > x0 + p.causal_off);
+        const int lim = res_row - p.causal_off - x0;  // column i visible iff i >= lim
+        const uint64_t* st_l = reinterpret_cast<const uint64_t*>(sStat + (s * 2 + 0) * kStr + w * 32);
+        const uint64_t* st_d = reinterpret_cast<const uint64_t*>(sStat + (s * 2 + 1) * kStr + w * 32);
+        uint32_t pa[16], da[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const uint64_t nl2 = st_l[i >> 1], nd2 = st_d[i >> 1];
+          float e0, e1;
+          f2_unpack(f2_fma(f2_pack(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1])), c2, nl2), e0, e1);
+          float p0 = fast_exp2(e0), p1 = fast_exp2(e1);
+          if (need_mask) {
+            if (i < lim) p0 = 0.f;
+            if (i + 1 < lim) p1 = 0.f;
+          }
+          float g0, g1;
+          f2_unpack(f2_mul(f2_pack(p0, p1), f2_add(f2_pack(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1])), nd2)), g0, g1);
+          pa[i >> 1] = pack_bf16(p0, p1);
+          da[i >> 1] = pack_bf16(g0, g1);
+        }
+        if (k > 0) {
+          mbar_wait(a_free, (k - 1) & 1, ctl, 0x680);
+          tc_fence_after_sync();
+        }
+        tmem_st16(ta, pa);
+        tmem_st16(ta + 32, da);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&a_full[0]);
+      }
+    } else
     for (int k = w; k < n_it; k += 2) {
-      const int s = k % NST, b = k % NBUF;
+      const int s = k % NS1, b = k % NBUF;
       const int x0 = (it_begin + k) * kStr;
-      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k / NST) & 1, ctl, 0x500 + s);
+      if constexpr (MODE == kDkDv) mbar_wait(&x_full[s], (k / NS1) & 1, ctl, 0x500 + s);
       mbar_wait(&t_full[w], (k >> 1) & 1, ctl, 0x600 + w);
       tc_fence_after_sync();
       const uint32_t t1 = tmem_base + lane_addr + b * 128, t2 = t1 + 64;
@@ -296,10 +401,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tmem_ld32(t2, s2);
       tmem_ld32(t2 + 32, s2 + 32);
       tmem_wait_ld();
-      if constexpr (C::kSplitA) {
-        tc_fence_before_sync();
-        mbar_arrive(t_read);
-      }
       // key n visible to query m iff n <= m + off
       bool need_mask;
       int lim;  // kDkDv: first visible column (query) index; kDq: last visible column (key) index
@@ -341,17 +442,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         pa[i >> 1] = pack_bf16(p0, p1);
         da[i >> 1] = pack_bf16(g0, g1);
       }
-      if constexpr (C::kSplitA) {
-        if (k > 0) {
-          mbar_wait(a_free, (k - 1) & 1, ctl, 0x680);
-          tc_fence_after_sync();
-        }
-        tmem_st32(tmem_base + lane_addr + C::kACol, pa);
-        tmem_st32(tmem_base + lane_addr + C::kACol + 32, da);
-      } else {
-        if constexpr (MODE == kDkDv) tmem_st32(t1, pa);
-        tmem_st32(t2, da);
-      }
+      if constexpr (MODE == kDkDv) tmem_st32(t1, pa);
+      tmem_st32(t2, da);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&a_full[w]);

@@ -145,16 +145,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
   const AbortCtl ctl{p.status, abort_flag};
 
-  const int head = blockIdx.y;
+  int tile_i, head;
+  launch_order(blockIdx.x, gridDim.x, p.causal != 0, tile_i, head);
   const int batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   int r0, it_begin, it_end;
   if constexpr (MODE == kDkDv) {
-    r0 = blockIdx.x * kT;  // first key; small r0 = most work, launched first
+    r0 = tile_i * kT;  // first key; small r0 = most work, launched first
     it_begin = p.causal ? max(0, r0 - p.causal_off) / kT : 0;
     it_end = (p.Sq + kT - 1) / kT;
   } else {
-    r0 = (gridDim.x - 1 - blockIdx.x) * kT;  // first query; late queries first
+    r0 = (gridDim.x - 1 - tile_i) * kT;  // first query; late queries first
     it_begin = 0;
     it_end = (p.Sk + kT - 1) / kT;
     if (p.causal) {

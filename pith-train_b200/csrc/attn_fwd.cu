@@ -32,7 +32,7 @@ struct FwdSmem {
   static constexpr int kBarOff = kVOff + VST * kVTile;
   static constexpr int kNumBars = 1 + 2 * KST + 2 * VST + 8;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
-  static constexpr int kAlloc = kTotal + 1024;  // slack for the 1024-byte alignment of the base
+  static constexpr int kAlloc = kTotal;  // no slack: the kernel checks that the dynamic window starts 1024-aligned
 };
 
 // S[128 x BN] = Q_tile[128 x DQK] * K_blk[BN x DQK]^T, both operands K-major in shared memory.
@@ -64,8 +64,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using L = FwdSmem<DQK, BN, KST, VST>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem + L::kQOff;
   uint8_t* sK = smem + L::kKOff;
   uint8_t* sV = smem + L::kVOff;
@@ -87,8 +86,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   const AbortCtl ctl{p.status, abort_flag};
 
   // Heaviest (latest) query tiles first.
-  const int qblk = gridDim.x - 1 - blockIdx.x;
-  const int head = blockIdx.y;
+  int tile_i, head;
+  launch_order(blockIdx.x, gridDim.x, p.causal != 0, tile_i, head);
+  const int qblk = gridDim.x - 1 - tile_i;
   const int batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int m0 = qblk * (2 * kBM);
@@ -123,6 +123,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if ((smem_u32(smem) & 1023u) != 0u) {  // the swizzled tiles need a 1024-byte aligned window
+    if (threadIdx.x == 0) report_error(ctl, 0xA1u, smem_u32(smem));
+    nblk[0] = nblk[1] = nmax = 0;
+  }
   if (*abort_flag != 0u) nblk[0] = nblk[1] = nmax = 0;
 
   // Register budget: the four warps of warpgroup 0 (producer, MMA issuer, two idle) need few registers,

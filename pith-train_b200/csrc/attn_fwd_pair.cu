@@ -92,8 +92,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFwdThreads, 1)
 
   // Heaviest (latest) query rows first.
   const int npairs = gridDim.x >> 1;
-  const int qpair = npairs - 1 - (blockIdx.x >> 1);
-  const int head = blockIdx.y;
+  int tile_i, head;
+  launch_order(blockIdx.x >> 1, npairs, p.causal != 0, tile_i, head);  // both CTAs of a pair map to the same (pair, head)
+  const int qpair = npairs - 1 - tile_i;
   const int batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int m_base = qpair * (4 * kBM);

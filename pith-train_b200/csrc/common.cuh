@@ -318,6 +318,28 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
+// Launch order. The grid is (tiles, heads, batch) and CTAs are dispatched x-fastest; the kernels number their tiles
+// heaviest first (causal), which balances one head but leaves the heavy tiles of the last heads for the end of the
+// launch. This maps the linear CTA index to (tile, head) so that heads go in groups of G = 8 with the tile index
+// outermost inside a group: the last group is short enough to be balanced by its own heavy-first order, and only G
+// heads' streamed tensors are hot in L2 at a time (32 heads x 8192^2 causal: forward 0.485 -> 0.431 ms, dK/dV pass
+// 0.861 -> 0.832 ms, dQ pass 0.622 -> 0.600 ms; groups of 4 measured the same).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void launch_order(int x, int tiles, bool causal, int& tile, int& head) {
+  const int H = gridDim.y;
+  const int G = (H % 8 == 0) ? 8 : (H % 4 == 0) ? 4 : (H % 2 == 0) ? 2 : 1;
+  if (!causal || G == 1) {  // equal tiles: nothing to balance
+    tile = x;
+    head = blockIdx.y;
+    return;
+  }
+  const int l = x + tiles * blockIdx.y;
+  const int g = l / (G * tiles), r = l - g * (G * tiles);
+  tile = r / G;
+  head = g * G + (r - tile * G);
+}
+
+// ---------------------------------------------------------------------------
 // Small helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float fast_exp2(float x) {
