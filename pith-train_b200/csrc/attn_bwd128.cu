@@ -1,8 +1,7 @@
 // Attention backward for head dimension 128 (GQA / MHA) on sm_100a.
 //
-// A tcgen05 MMA with M = 128 costs the same 64 cycles per K-step of 16 whether it is 128, 64 or 32
-// columns wide, so every GEMM here is 128 x 128: a 128-row tile is resident for the whole CTA and
-// 128-row tiles stream past it. TMEM then has room for exactly one pair of score tiles next to the
+// A tcgen05 MMA with M = 128 and K = 16 costs 64 cycles at N = 128 and still 48 at N = 64 (measured), so
+// every GEMM here is 128 x 128: a 128-row tile is resident for the whole CTA and 128-row tiles stream past it. TMEM then has room for exactly one pair of score tiles next to the
 // accumulators, so instead of double-buffering the scores the four GEMMs of an iteration are
 // interleaved with the next iteration's so that the tensor core always has a GEMM to run while the
 // 256 compute threads are in the exponentials:
@@ -10,6 +9,7 @@
 //   mode kDkDv (resident K_n, V_n; streamed Q_i, dO_i; lane = key, column = query)
 //     MMA order   S^T(0) dP^T(0) | dV(0) S^T(1) dK(0) dP^T(1) | dV(1) S^T(2) dK(1) dP^T(2) | ...
 //     compute     P^T(k) = exp2(S^T c - lse) after S^T(k)      -> bf16 into T1, feeds dV(k) = P^T dO_i
+//                 (stored in two halves: dV(k) starts on the first while the second is in the exponentials)
 //                 dS^T(k) = P^T (dP^T - delta) after dP^T(k)   -> bf16 into T2, feeds dK(k) = dS^T Q_i
 //   mode kDq (resident Q_m, dO_m; streamed K_j, V_j; lane = query, column = key)
 //     MMA order   S(0) dP(0) | S(1) dQ(0) dP(1) | S(2) dQ(1) dP(2) | ...
@@ -54,8 +54,9 @@ struct Smem {
   static constexpr int kX1Off = kR2Off + kTile;
   static constexpr int kX2Off = kX1Off + kNS1 * kTile;
   static constexpr int kStatOff = kX2Off + kNS2 * kTile;  // [2][2][128] floats: a two-deep ring of its own
-  static constexpr int kBarOff = kStatOff + 2 * 2 * kT * 4;
-  static constexpr int kNumBars = 1 + 4 * kMaxST + 6 + 4;
+  static constexpr int kFlagOff = kStatOff + 2 * 2 * kT * 4;
+  static constexpr int kBarOff = kFlagOff + 8;
+  static constexpr int kNumBars = 1 + 4 * kMaxST + 7 + 4;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
   static constexpr int kAlloc = kTotal;  // no slack: the kernel checks that the dynamic window starts 1024-aligned
 };
@@ -76,12 +77,17 @@ __device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_
   }
 }
 // D[128 x 128] (+)= A[128 x 128] (packed bf16 in TMEM, halves at columns +0 and +64) * B (MN-major tile in shared memory)
+// PART 0: all eight K-steps; 1: K-steps {0,1,4,5} (the first half of every thread's packed columns); 2: {2,3,6,7},
+// always accumulating.
+template <int PART = 0>
 __device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool acc,
                                         bool leader) {
 #pragma unroll
   for (int kk = 0; kk < kT / 16; ++kk) {
+    if (PART == 1 && (kk & 2)) continue;
+    if (PART == 2 && !(kk & 2)) continue;
     const uint32_t a = a_tmem + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-    if (leader) umma_ts(d_tmem, a, desc_advance(bdesc, kk * 2048), idesc, (acc || kk > 0) ? 1u : 0u);
+    if (leader) umma_ts(d_tmem, a, desc_advance(bdesc, kk * 2048), idesc, (PART == 2 || acc || kk > 0) ? 1u : 0u);
   }
 }
 
@@ -118,6 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* sX1 = smem + Smem::kX1Off;
   uint8_t* sX2 = smem + Smem::kX2Off;
   float* sStat = reinterpret_cast<float*>(smem + Smem::kStatOff);
+  volatile int* sFlag = reinterpret_cast<volatile int*>(smem + Smem::kFlagOff);  // [2], per statistics stage
   constexpr int NS1 = kNS1;
   constexpr int NS2 = (MODE == kDq) ? kNS2 + 1 : kNS2;
   auto x1_stage = [&](int st) { return sX1 + st * kTile; };
@@ -136,7 +143,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* ds_full = p_full + 1;   // dS is in TMEM
   uint64_t* acc_full = ds_full + 1;
   uint64_t* rt_full = acc_full + 1;  // kDq: resident tiles are in TMEM
-  uint64_t* st_full = rt_full + 1;   // kDkDv: statistics of the streamed queries (two stages)
+  uint64_t* ph_full = rt_full + 1;   // kDkDv: the first half of every thread's P^T columns is in TMEM
+  uint64_t* st_full = ph_full + 1;   // kDkDv: statistics of the streamed queries (two stages)
   uint64_t* st_empty = st_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Smem::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -181,6 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(ds_full, 256);
     mbar_init(acc_full, 1);
     mbar_init(rt_full, 256);
+    mbar_init(ph_full, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&st_full[i], 1);
       mbar_init(&st_empty[i], 256);
@@ -263,6 +272,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             sStat[(ss * 2 + 0) * kT + j * 32 + lane] = (rl[j] == -INFINITY) ? -INFINITY : -rl[j];
             sStat[(ss * 2 + 1) * kT + j * 32 + lane] = -rd[j];
           }
+          const bool finite = __all_sync(0xFFFFFFFFu, rl[0] != -INFINITY && rl[1] != -INFINITY && rl[2] != -INFINITY &&
+                                                          rl[3] != -INFINITY);
+          if (lane == 0) sFlag[ss] = finite ? 1 : 0;
           __syncwarp();
           if (lane == 0) mbar_arrive(&st_full[ss]);
           load_stats(k + 2, rl, rd);  // consumed two steps from now
@@ -331,9 +343,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t ph2 = static_cast<uint32_t>((k + 1) / NS2) & 1u;
         const bool more = k + 1 < n_it;
         if constexpr (MODE == kDkDv) {
+          mbar_wait(ph_full, k & 1, ctl, 0x480);
+          tc_fence_after_sync();
+          gemm_ts<1>(tmem_base + kColAcc, t1, pick2(x2m, s2), idesc_mn, k > 0, leader);  // dV += P^T dO_i, first half
           mbar_wait(p_full, k & 1, ctl, 0x400);
           tc_fence_after_sync();
-          gemm_ts(tmem_base + kColAcc, t1, pick2(x2m, s2), idesc_mn, k > 0, leader);  // dV += P^T dO_i
+          gemm_ts<2>(tmem_base + kColAcc, t1, pick2(x2m, s2), idesc_mn, true, leader);
           if (leader) umma_commit(&x2_empty[s2]);  // last use of dO_i
           if (more) {
             mbar_wait(&x_full[sn1], ph1, ctl, 0x300 + sn1);
@@ -430,12 +445,21 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_before_sync();
         mbar_arrive(p_full);
       }
-      // Two copies of the loop (a run-time test inside it costs more than it saves): in the dQ pass every fourth pair
-      // of exponentials runs on the FMA pipe unless the warp holds a row without keys, which needs the MUFU's exact 0.
-      auto p_block = [&](auto emu_tag) {
-        constexpr bool EMU = decltype(emu_tag)::value;
+      // Masked scores become -inf before the loop, so that the loop itself carries no mask test.
+      if (need_mask) {
 #pragma unroll
-      for (int i = 0; i < 64; i += 4) {
+        for (int j = 0; j < 64; ++j)
+          if (MODE == kDkDv ? (j < lim) : (j > lim)) pv[j] = 0xFF800000u;
+      }
+      // Two copies of the loop (a run-time test inside it costs more than it saves): every fourth (dQ pass) or third
+      // (dK/dV pass) pair of exponentials runs on the FMA pipe, unless the tile is masked or holds a row without keys:
+      // those need the MUFU's exact 0 for -inf. Measured per tile: 1230 -> 1030 cycles for the 64 exponentials of a
+      // thread, which the 16-per-clock MUFU otherwise bounds at 1024.
+      auto p_block = [&](auto emu_tag, auto half_tag) {
+        constexpr bool EMU = decltype(emu_tag)::value;
+        constexpr int I0 = decltype(half_tag)::value * 32;
+#pragma unroll
+      for (int i = I0; i < I0 + 32; i += 4) {
         uint64_t nl2[2];
         if constexpr (MODE == kDkDv) {
           const ulonglong2 lv = st_l[i >> 2];
@@ -449,33 +473,40 @@ __global__ void __launch_bounds__(kThreads, 1)
           float a0, a1;
           f2_unpack(f2_fma(f2_pack(__uint_as_float(pv[j]), __uint_as_float(pv[j + 1])), c2, nl2[u]), a0, a1);
           float p0, p1;
-          if (EMU && ((j >> 1) & 3) == 0) {
+          constexpr int kEvery = (MODE == kDq) ? 4 : 3;  // one pair in kEvery runs on the FMA pipe
+          if (EMU && ((j >> 1) % kEvery) == 0) {
             exp2_poly2(a0, a1, p0, p1);
           } else {
             p0 = fast_exp2(a0);
             p1 = fast_exp2(a1);
-          }
-          if (need_mask) {
-            if constexpr (MODE == kDkDv) {
-              if (j < lim) p0 = 0.f;
-              if (j + 1 < lim) p1 = 0.f;
-            } else {
-              if (j > lim) p0 = 0.f;
-              if (j + 1 > lim) p1 = 0.f;
-            }
           }
           pv[j] = __float_as_uint(p0);
           pv[j + 1] = __float_as_uint(p1);
         }
       }
       };
-      if (MODE == kDq && emu_ok) p_block(std::true_type{});
-      else p_block(std::false_type{});
-      if constexpr (MODE == kDkDv) {
-        uint32_t pa[32];
+      bool emu_now = emu_ok && !need_mask;
+      if constexpr (MODE == kDkDv) emu_now = sFlag[s] != 0 && !need_mask;  // every query of the tile has a finite lse
+      using H0 = std::integral_constant<int, 0>;
+      using H1 = std::integral_constant<int, 1>;
+      if (emu_now) p_block(std::true_type{}, H0{});
+      else p_block(std::false_type{}, H0{});
+      if constexpr (MODE == kDkDv) {  // first half of this thread's columns: dV may start on it
+        uint32_t pa[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) pa[i] = pack_bf16(__uint_as_float(pv[2 * i]), __uint_as_float(pv[2 * i + 1]));
-        tmem_st32(t1, pa);
+        for (int i = 0; i < 16; ++i) pa[i] = pack_bf16(__uint_as_float(pv[2 * i]), __uint_as_float(pv[2 * i + 1]));
+        tmem_st16(t1, pa);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(ph_full);
+      }
+      if (emu_now) p_block(std::true_type{}, H1{});
+      else p_block(std::false_type{}, H1{});
+      if constexpr (MODE == kDkDv) {
+        uint32_t pa[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pa[i] = pack_bf16(__uint_as_float(pv[32 + 2 * i]), __uint_as_float(pv[32 + 2 * i + 1]));
+        tmem_st16(t1 + 16, pa);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(p_full);

@@ -379,9 +379,9 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
 // 2^x for a pair of floats on the FMA pipe instead of the MUFU: x = n + f with n = round(x), |f| <= 0.5, 2^f by a
 // degree-3 polynomial (relative error below 8e-5, far inside the bf16 rounding the results get), n added to the
 // exponent field. Inputs are clamped to >= -125 (the result stays a normal number, about 2e-38): callers that need an
-// exact 0 for -inf (masked scores, rows without any visible key) must take the MUFU path for those. The dQ pass routes
-// a quarter of its exponentials through it (measured: 3-5 % faster at 25 %, no better at 50 %); in the forward and the
-// dK/dV pass it measured no gain once the issue path had been fixed, so they keep the MUFU.
+// exact 0 for -inf (masked scores, rows without any visible key) must take the MUFU path for those. The backward passes
+// route a quarter (dQ) or a third (dK/dV) of their exponentials through it: the MUFU's 16 results per clock otherwise
+// bound the 16384 exponentials of a tile at 1024 cycles. The forward measured no gain and keeps the MUFU.
 __device__ __forceinline__ void exp2_poly2(float x0, float x1, float& p0, float& p1) {
   const uint64_t x2 = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
   const uint64_t magic = f2_pack(12582912.f, 12582912.f), nmagic = f2_pack(-12582912.f, -12582912.f);  // 1.5 * 2^23
