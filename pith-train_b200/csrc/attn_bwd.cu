@@ -639,11 +639,11 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   };
   // Side by side pays when a launch is only a few waves long (its partial last wave is a large share); on long
   // launches of the head_dim-128 kernels the two kernels' interleaved CTAs cost more in L2 locality than the tail
-  // gives back (measured, 32 heads: 4096 x 4096 causal 0.615 -> 0.563 ms, 6144 x 6144 causal 1.257 -> 1.152 ms,
-  // 8192 x 8192 causal 1.90 -> 2.01 ms). The Dqk = 192 kernels gain at every size measured (16 heads,
-  // 8192 x 8192 causal: 1.777 -> 1.636 ms).
+  // gives back (measured, 32 heads: 4096 x 2048 non-causal 0.437 -> 0.421 ms, 4096 x 4096 causal 0.439 -> 0.433 ms,
+  // 6144 x 6144 causal 0.889 -> 0.932 ms, 8192 x 8192 causal 1.52 -> 1.68 ms). The Dqk = 192 kernels gain at every
+  // size measured (16 heads, 8192 x 8192 causal: 1.052 -> 1.018 ms).
   const double work = static_cast<double>(a->B) * a->Hq * a->Sq * a->Sk * (a->causal ? 0.5 : 1.0);
-  const double limit = a->Dqk == 128 ? 7.0e8 : 4.0e9;
+  const double limit = a->Dqk == 128 ? 4.5e8 : 4.0e9;
   const bool side_by_side = (a->flags & PITH_BWD_CONCURRENT) || (!(a->flags & PITH_BWD_SERIAL) && work <= limit);
   if (!(want_dkv && want_dq) || !side_by_side) {
     if (want_dkv)
