@@ -629,6 +629,7 @@ extern "C" int pith_attn_bwd(const pith_attn_bwd_args* a, void* stream) {
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal ? 1 : 0; p.causal_off = a->causal_offset;
   p.dq_store_bf16 = dq_bf16 ? 1 : 0;
+  p.hpc = 1;
   p.scale = a->softmax_scale; p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
   for (int i = 0; i < 3; ++i) { p.dqs[i] = a->dq_stride[i]; p.dks[i] = a->dk_stride[i]; p.dvs[i] = a->dv_stride[i]; }
   for (int i = 0; i < 2; ++i) { p.ls[i] = a->lse_stride[i]; p.dls[i] = a->delta_stride[i]; }

@@ -153,8 +153,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = threadIdx.x & 31;
   const AbortCtl ctl{p.status, abort_flag};
 
-  int tile_i, head;
-  launch_order(blockIdx.x, gridDim.x, p.causal != 0, tile_i, head);
+  // kDkDv: one CTA walks the query tiles of `hpc` consecutive query heads of one GQA group (same K_n, V_n, same
+  // accumulators): fewer prologues and fewer fp32 write-outs per unit of work. `head` is the first of them.
+  const int hpc = (MODE == kDkDv) ? p.hpc : 1;
+  int tile_i, head_i;
+  launch_order(blockIdx.x, gridDim.x, p.causal != 0, tile_i, head_i);
+  const int head = head_i * hpc;
   const int batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   int r0, it_begin, it_end;
@@ -171,7 +175,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       it_end = last_key < 0 ? 0 : min(it_end, last_key / kT + 1);
     }
   }
-  int n_it = max(0, it_end - it_begin);
+  const int n_tile = max(0, it_end - it_begin);  // streamed tiles per head
+  const int n_div = max(n_tile, 1);
+  int n_it = n_tile * hpc;
 
   if (threadIdx.x == 0) {
     // a launch that finds an error already recorded (by an earlier CTA or launch) does no work
@@ -211,7 +217,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (*abort_flag != 0u) n_it = 0;
 
   const int r1_head = (MODE == kDkDv) ? kv_head : head;  // head index of the resident tensors
-  const int x_head = (MODE == kDkDv) ? head : kv_head;   // head index of the streamed tensors
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -234,22 +239,23 @@ __global__ void __launch_bounds__(kThreads, 1)
       // stage as -lse (-inf where the row does not exist or saw no key) and -delta.
       auto load_stats = [&](int k, float (&rl)[4], float (&rd)[4]) {
         if constexpr (MODE == kDkDv) {
-          const int x0 = (it_begin + k) * kT;
+          const int hs = k / n_div, x0 = (it_begin + k - hs * n_tile) * kT;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int m = x0 + j * 32 + lane;
             rl[j] = -INFINITY;
             rd[j] = 0.f;
             if (k < n_it && m < p.Sq) {
-              rl[j] = p.lse[batch * p.ls[0] + head * p.ls[1] + m];
-              rd[j] = p.delta[batch * p.dls[0] + head * p.dls[1] + m];
+              rl[j] = p.lse[batch * p.ls[0] + (head + hs) * p.ls[1] + m];
+              rd[j] = p.delta[batch * p.dls[0] + (head + hs) * p.dls[1] + m];
             }
           }
         }
       };
       auto step = [&](int k, float (&rl)[4], float (&rd)[4]) {
         const int s1 = k % NS1, s2 = k % NS2;
-        const int x0 = (it_begin + k) * kT;
+        const int hs = k / n_div, x0 = (it_begin + k - hs * n_tile) * kT;
+        const int x_head = (MODE == kDkDv) ? head + hs : kv_head;  // head index of the streamed tensors
         if (lane == 0) {
           if (MODE == kDq && k == kNS2) mbar_wait(rt_full, 0, ctl, 0x1F0);  // the resident tiles' memory is free now
           mbar_wait(&x_empty[s1], ((k / NS1) & 1) ^ 1, ctl, 0x100 + s1);
@@ -420,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int k = 0; k < n_it; ++k) {
       const int s = k & 1;  // statistics stage (mode kDkDv, two-deep ring)
-      const int x0 = (it_begin + k) * kT + h * 64;  // global position of this thread's first column
+      const int x0 = (it_begin + k - (k / n_div) * n_tile) * kT + h * 64;  // global position of this thread's first column
       if constexpr (MODE == kDkDv) mbar_wait(&st_full[s], (k >> 1) & 1, ctl, 0x600 + s);
       const ulonglong2* st_l = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 0) * kT + h * 64);
       const ulonglong2* st_d = reinterpret_cast<const ulonglong2*>(sStat + (s * 2 + 1) * kT + h * 64);
@@ -643,8 +649,40 @@ static int launch(const pith_attn_bwd_args* a, const BwdParams& p, cudaStream_t 
   auto kern = attn_bwd128_kernel<MODE>;
   PITH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kAlloc));
   if (MODE == kDkDv) {
-    dim3 grid((a->Sk + kT - 1) / kT, a->Hq, a->B);
-    kern<<<grid, kThreads, Smem::kAlloc, st>>>(tk, tv, tq, tdo, p);
+    // Query heads of one GQA group per CTA (1, 2 or 4): each CTA pays ~1700 cycles of prologue and ~8700 of fp32
+    // write-out around ~2650 cycles per streamed tile, so fewer, longer CTAs win as long as the launch stays balanced.
+    // Non-causal: all CTAs are equal, the cost is waves x CTA length. Causal: CTAs go heaviest first, the cost is the
+    // work per SM as long as the heaviest CTA stays below 0.6 of it.
+    const int tiles = (a->Sk + kT - 1) / kT, qtiles = (a->Sq + kT - 1) / kT, group = a->Hq / a->Hkv;
+    constexpr double kIter = 2650.0, kFixed = 10400.0, kSMs = 148.0;
+    double iters = 0.0, heaviest = 0.0;  // streamed tiles over the key tiles of one head; of the heaviest key tile
+    for (int t = 0; t < tiles; ++t) {
+      const int first = a->causal ? (t * kT - a->causal_offset > 0 ? (t * kT - a->causal_offset) / kT : 0) : 0;
+      const double n = qtiles > first ? qtiles - first : 0;
+      iters += n;
+      heaviest = n > heaviest ? n : heaviest;
+    }
+    BwdParams pk = p;
+    pk.hpc = 1;
+    double best = 0.0;
+    for (int hpc = 1; hpc <= 4; hpc *= 2) {
+      if (group % hpc != 0) break;
+      const double ctas = static_cast<double>(tiles) * a->Hq * a->B / hpc;
+      double cost;
+      if (!a->causal) {
+        const double waves = static_cast<double>(static_cast<int64_t>((ctas + kSMs - 1) / kSMs));
+        cost = waves * (hpc * heaviest * kIter + kFixed);
+      } else {
+        cost = (static_cast<double>(a->Hq) * a->B * iters * kIter + ctas * kFixed) / kSMs;
+        if (hpc > 1 && hpc * heaviest * kIter > 0.6 * cost) break;
+      }
+      if (hpc == 1 || cost < best) {
+        best = cost;
+        pk.hpc = hpc;
+      }
+    }
+    dim3 grid(tiles, a->Hq / pk.hpc, a->B);
+    kern<<<grid, kThreads, Smem::kAlloc, st>>>(tk, tv, tq, tdo, pk);
   } else {
     dim3 grid((a->Sq + kT - 1) / kT, a->Hq, a->B);
     kern<<<grid, kThreads, Smem::kAlloc, st>>>(tq, tdo, tk, tv, p);

@@ -18,6 +18,7 @@ struct BwdParams {
   uint32_t* status;
   int B, Sq, Sk, Hq, Hkv;
   int causal, causal_off;
+  int hpc;            // head_dim-128 dK/dV pass: query heads per CTA (set by its launcher)
   int dq_store_bf16;  // dq_acc points at a bf16 [B][Sq][Hq][D] OUTPUT that the dQ pass stores (dqs in bf16 elements)
   float scale_log2, scale;
   int64_t dqs[3], dks[3], dvs[3];
