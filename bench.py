@@ -62,7 +62,7 @@ def peaks():
 # DRAM read + write bytes per launch of a kernel at an exact workload, taken from the ncu summary committed beside
 # it. Keyed by (workload, n_gpus, kernel substring); anything else reports null.
 NCU_TRAFFIC = {
-    ("qwen3", 1, "dK/dV"): (210.4e6, "profiles/attention_kernels_qwen3_s8192.md (attn_bwd128_kernel<kDkDv>, S = 8192)"),
+    ("qwen3", 1, "dK/dV"): (343.2e6, "profiles/attention_kernels_qwen3_s8192.md (attn_bwd128_kernel<kDkDv>, S = 8192)"),
 }
 
 
