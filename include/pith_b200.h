@@ -20,6 +20,8 @@
  *  - Return value: 0 = enqueued; negative = rejected on the host (pith_last_error() has the
  *    text). Device-side anomalies (a bounded wait that ran out) are written to *status
  *    (a zero-initialised device uint32, optional) as (code << 24 | detail); see pith_status_string.
+ *    Codes: 1 a barrier wait inside a kernel ran out, 2 unexpected TMEM allocation, 3 a wait for a ring neighbour
+ *    ran out, 4 a kernel found its shared-memory window misaligned. A launch that finds the word non-zero does no work.
  *  - Re-entrant; no internal threads; no global mutable state besides, per device, one side stream with two
  *    events used by pith_attn_bwd (created on first use) and the device address of the scratch area of
  *    pith_attn_bwd_noalloc (looked up on its first call; it does not survive cudaDeviceReset).

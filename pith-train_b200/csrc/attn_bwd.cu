@@ -387,7 +387,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         tc_fence_before_sync();
         mbar_arrive(&a_full[0]);
       }
-    } else
+    } else {
+    // two buffers: the groups alternate iterations
     for (int k = w; k < n_it; k += 2) {
       const int s = k % NS1, b = k % NBUF;
       const int x0 = (it_begin + k) * kStr;
@@ -447,6 +448,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&a_full[w]);
+    }
     }
 
     // ---- write-out: accumulators -> scaled fp32 atomics

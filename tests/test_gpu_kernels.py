@@ -306,6 +306,38 @@ def test_full_size_against_flash_attn(qwen3_full):
     assert_bf16_close(K.cast_to_bf16(f["dv"]), v.grad, "dV vs flash-attn")
 
 
+# Launches long enough for the dK/dV pass to give one CTA several query heads of a GQA group (its launcher picks 1, 2
+# or 4 by a cost model; the small cases above always get 1): a 2:1 group over a long causal launch takes 2, the
+# non-causal ring-step shapes of the 8:1 Qwen3 group take 4.
+@pytest.mark.parametrize("Sq,Sk,Hq,Hkv,causal", [(4096, 4096, 32, 16, True), (2048, 4096, 32, 4, False),
+                                                 (4096, 2048, 32, 4, False)])
+def test_several_heads_per_cta_against_flash_attn_and_oracle(K, cuda_device, Sq, Sk, Hq, Hkv, causal):
+    fa = pytest.importorskip("flash_attn")
+    q, k, v, do = _inputs(1, Sq, Sk, Hq, Hkv, 128, cuda_device, seed=7)
+    scale = 128 ** -0.5
+    out, lse = K.attn_fwd(q, k, v, scale, causal, 0)
+    delta = K.bwd_preprocess(out, do)
+    dq, dk, dv = (torch.zeros(t.shape, device=cuda_device) for t in (q, k, v))
+    K.attn_bwd(q, k, v, do, lse, delta, scale, causal, 0, dq, dk, dv)
+    K.check_device_status(cuda_device)
+    qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
+    ro = fa.flash_attn_func(qr, kr, vr, softmax_scale=scale, causal=causal)
+    ro.backward(do)
+    assert_bf16_close(out, ro, "O vs flash-attn")
+    assert_bf16_close(K.cast_to_bf16(dq), qr.grad, "dQ vs flash-attn")
+    assert_bf16_close(K.cast_to_bf16(dk), kr.grad, "dK vs flash-attn")
+    assert_bf16_close(K.cast_to_bf16(dv), vr.grad, "dV vs flash-attn")
+    # the last 128 keys of the last kv head against the oracle: every query head of its group adds into them
+    g = Hq // Hkv
+    heads = list(range(Hq - g, Hq))
+    q0 = Sq - 128 if causal else 0  # causal: only the last 128 queries see those keys
+    dl = O.delta(out[:, q0:, heads].cpu().float(), do[:, q0:, heads].cpu())
+    _, rdk, rdv = O.attention_bwd(q[:, q0:, heads].cpu(), k[:, -128:, -1:].cpu(), v[:, -128:, -1:].cpu(),
+                                  do[:, q0:, heads].cpu(), lse[:, heads, q0:].cpu(), dl, scale, causal, 0)
+    assert_bf16_close(dk[:, -128:, -1:], rdk, "dK[-128:] vs oracle")
+    assert_bf16_close(dv[:, -128:, -1:], rdv, "dV[-128:] vs oracle")
+
+
 # ----------------------------------------------------------------------------- q/k RMSNorm + rotary embedding
 def _qk_golden(dev):
     import numpy as np
