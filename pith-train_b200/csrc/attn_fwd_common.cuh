@@ -51,6 +51,7 @@ __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const Abort
   const float c = p.scale_log2;
   float m_used = -INFINITY;
   float l = 0.f;
+  const int64_t po_off = batch * p.pos[0] + static_cast<int64_t>(row) * p.pos[1] + head * p.pos[2];
   for (int j = 0; j < nb; ++j) {
     mbar_wait(s_full, j & 1, ctl, 0x700 + tag);
     tc_fence_after_sync();
@@ -128,16 +129,26 @@ __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const Abort
   }
 
   // ---- epilogue: normalise, optional merge with a previous partial, store
+  const bool row_ok = row < p.Sq;
+  // the previous partial's LSE and first 32 columns are requested before the wait for the last PV GEMM; each later
+  // chunk is requested before the chunk in front of it is processed
+  const bool merge = p.prev_o != nullptr;
+  float pl = -INFINITY;
+  float4 pq[8];
+  const float4* pp = reinterpret_cast<const float4*>(p.prev_o + po_off);
+  if (merge && row_ok) {
+    pl = p.prev_lse[batch * p.pls[0] + head * p.pls[1] + row];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pq[i] = pp[i];
+  }
   if (nb > 0) {
     mbar_wait(o_full, 0, ctl, 0x800 + tag);
     tc_fence_after_sync();
   }
-  const bool row_ok = row < p.Sq;
   float inv = (l > 0.f) ? 1.0f / l : 0.f;
   float lse2 = (l > 0.f) ? fmaf(m_used, c, fast_log2(l)) : -INFINITY;
   float w_prev = 0.f;
-  if (p.prev_o != nullptr) {
-    const float pl = row_ok ? p.prev_lse[batch * p.pls[0] + head * p.pls[1] + row] : -INFINITY;
+  if (merge) {
     const float mx = fmaxf(pl, lse2);
     if (mx > -INFINITY) {
       const float e1 = exp2f(pl - mx), e2 = exp2f(lse2 - mx);
@@ -149,7 +160,6 @@ __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const Abort
   }
   if (row_ok) p.lse[batch * p.ls[0] + head * p.ls[1] + row] = p.lse_natural ? lse2 * 0.6931471805599453f : lse2;
   const int64_t o_off = batch * p.os[0] + static_cast<int64_t>(row) * p.os[1] + head * p.os[2];
-  const int64_t po_off = batch * p.pos[0] + static_cast<int64_t>(row) * p.pos[1] + head * p.pos[2];
 #pragma unroll
   for (int cchunk = 0; cchunk < kDV / 32; ++cchunk) {
     uint32_t orr[32];
@@ -164,11 +174,17 @@ __device__ __forceinline__ void fwd_softmax_rows(const FwdParams& p, const Abort
       float ov[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) ov[i] = __uint_as_float(orr[i]) * inv;
-      if (p.prev_o != nullptr) {
-        const float4* pp = reinterpret_cast<const float4*>(p.prev_o + po_off + cchunk * 32);
+      if (merge) {
+        float4 cur[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) cur[i] = pq[i];
+        if (cchunk + 1 < kDV / 32) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) pq[i] = pp[(cchunk + 1) * 8 + i];
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float4 x = pp[i];
+          const float4 x = cur[i];
           ov[4 * i] = fmaf(w_prev, x.x, ov[4 * i]);
           ov[4 * i + 1] = fmaf(w_prev, x.y, ov[4 * i + 1]);
           ov[4 * i + 2] = fmaf(w_prev, x.z, ov[4 * i + 2]);
