@@ -172,6 +172,34 @@ typedef struct pith_combine_args {
  */
 int pith_combine(const pith_combine_args* args, void* stream);
 
+#define PITH_MAX_PARTIALS 16
+
+typedef struct pith_partial {
+  const void* o;         /* [B][rows][H][D] bf16: attention of query rows [row_begin, row_begin + rows) over one K/V block */
+  const float* lse;      /* [B][H][rows] fp32, log2 domain, unit stride along rows */
+  int32_t row_begin, rows;
+  int64_t o_stride[3];   /* b, s, h strides in elements */
+  int64_t lse_stride[2]; /* b, h strides in elements */
+} pith_partial;
+
+typedef struct pith_combine_partials_args {
+  pith_partial part[PITH_MAX_PARTIALS];
+  int32_t n;             /* 1 .. PITH_MAX_PARTIALS */
+  int32_t B, S, H, D;
+  void* out;             /* [B][S][H][D] bf16, contiguous */
+  float* lse;            /* [B][H][S] fp32, contiguous, log2 domain */
+} pith_combine_partials_args;
+
+/*
+ * Online-softmax merge of up to 16 partial attention results in one pass: every output row is the LSE-weighted mean
+ * of the partials that cover it (a row no partial covers, or whose partials all saw no key, gives O = 0, LSE = -inf).
+ * Weights and sums are fp32; O is rounded to bf16 once. The forward ring writes one bf16 partial per step and merges
+ * them here, instead of carrying an fp32 running result through every step's epilogue.
+ * Replaces: the chain of `_online_softmax_combine` / `_online_softmax_combine_log2` calls over the ring steps
+ *   (pithtrain/operators/ring_attention/standard.py:94, mla.py:68) and the final `.to(q.dtype)` (standard.py:104).
+ */
+int pith_combine_partials(const pith_combine_partials_args* args, void* stream);
+
 /* Size of the scratch area built into the library for pith_attn_bwd_noalloc (per GPU, held until exit). */
 #define PITH_NOALLOC_SCRATCH_BYTES (32u << 20)
 

@@ -1,5 +1,6 @@
 // HBM-bound kernels of the ring-attention path: the online-softmax merge of two partial
-// results, delta = rowsum(O * dO), and the final fp32 -> bf16 rounding of an accumulator.
+// results, of up to 16 partial results in one pass, delta = rowsum(O * dO), and the final fp32 -> bf16 rounding of
+// an accumulator.
 // Each thread moves 8 consecutive elements of one [b][s][h] row with 16-byte accesses.
 // The grid is (blocks per plane, H, B): a block stays inside one (batch, head) plane and walks
 // consecutive s, so the row data and the [B][H][S] statistics are read and written in whole
@@ -83,6 +84,60 @@ __global__ void __launch_bounds__(256) combine_kernel(const CombineParams p) {
     dst[0] = make_float4(o[0], o[1], o[2], o[3]);
     dst[1] = make_float4(o[4], o[5], o[6], o[7]);
     if (d0 == 0) lsep[s] = lse;
+  }
+}
+
+struct PartialsParams {
+  const __nv_bfloat16* o[PITH_MAX_PARTIALS];
+  const float* lse[PITH_MAX_PARTIALS];
+  int row_begin[PITH_MAX_PARTIALS], rows[PITH_MAX_PARTIALS];
+  int64_t os[PITH_MAX_PARTIALS][3];
+  int64_t ls[PITH_MAX_PARTIALS][2];
+  int n;
+  __nv_bfloat16* out;
+  float* lse_out;
+  int B, S, H, D;
+};
+
+// One pass over the output: a thread owns 8 columns of a row, reads the LSEs of the partials that cover the row
+// (once for the maximum, once with the data), and writes the weighted mean as bf16.
+__global__ void __launch_bounds__(256) combine_partials_kernel(const __grid_constant__ PartialsParams p) {
+  const uint32_t chunks = static_cast<uint32_t>(p.D) >> 3;
+  const uint32_t plane = static_cast<uint32_t>(p.S) * chunks;
+  const int h = blockIdx.y, b = blockIdx.z;
+  __nv_bfloat16* outp = p.out + (static_cast<int64_t>(b) * p.S * p.H + h) * p.D;
+  float* lsep = p.lse_out + (static_cast<int64_t>(b) * p.H + h) * p.S;
+  const int64_t out_row = static_cast<int64_t>(p.H) * p.D;
+  for (uint32_t item = blockIdx.x * 256u + threadIdx.x; item < plane; item += gridDim.x * 256u) {
+    const int s = static_cast<int>(item / chunks);
+    const uint32_t d0 = (item - static_cast<uint32_t>(s) * chunks) << 3;
+    float mx = -INFINITY;
+    for (int t = 0; t < p.n; ++t) {
+      const int r = s - p.row_begin[t];
+      if (r >= 0 && r < p.rows[t]) mx = fmaxf(mx, __ldg(p.lse[t] + b * p.ls[t][0] + h * p.ls[t][1] + r));
+    }
+    float den = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (mx > -INFINITY) {
+      for (int t = 0; t < p.n; ++t) {
+        const int r = s - p.row_begin[t];
+        if (r < 0 || r >= p.rows[t]) continue;
+        const float l = __ldg(p.lse[t] + b * p.ls[t][0] + h * p.ls[t][1] + r);
+        if (l == -INFINITY) continue;
+        const float w = exp2f(l - mx);
+        const Vec8 a = load8<false>(p.o[t], b * p.os[t][0] + r * p.os[t][1] + h * p.os[t][2] + d0);
+        den += w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, a.v[i], acc[i]);
+      }
+    }
+    const float inv = den > 0.f ? 1.0f / den : 0.f;
+    uint4 u;
+    u.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+    u.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+    u.z = pack_bf16(acc[4] * inv, acc[5] * inv);
+    u.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+    *reinterpret_cast<uint4*>(outp + s * out_row + d0) = u;
+    if (d0 == 0) lsep[s] = den > 0.f ? mx + log2f(den) : -INFINITY;
   }
 }
 
@@ -203,6 +258,41 @@ extern "C" int pith_combine(const pith_combine_args* a, void* stream) {
     case 6: combine_kernel<true, true, false><<<grid, 256, 0, st>>>(p); break;
     default: combine_kernel<true, true, true><<<grid, 256, 0, st>>>(p); break;
   }
+  PITH_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+extern "C" int pith_combine_partials(const pith_combine_partials_args* a, void* stream) {
+  PITH_REQUIRE(a != nullptr, "null args");
+  PITH_REQUIRE(a->n >= 1 && a->n <= PITH_MAX_PARTIALS, "n = %d partials (1 .. %d)", a->n, PITH_MAX_PARTIALS);
+  PITH_REQUIRE(a->B >= 0 && a->S >= 0 && a->H >= 0 && a->D > 0 && a->D % 8 == 0, "bad shape %dx%dx%dx%d", a->B, a->S,
+               a->H, a->D);
+  if (static_cast<int64_t>(a->B) * a->S * a->H == 0) return kOk;
+  PITH_REQUIRE(a->out && a->lse && aligned16(a->out), "out must be a 16-byte aligned pointer, lse non-null");
+  PartialsParams p;
+  for (int t = 0; t < a->n; ++t) {
+    const pith_partial& q = a->part[t];
+    PITH_REQUIRE(q.rows >= 0 && q.row_begin >= 0 && static_cast<int64_t>(q.row_begin) + q.rows <= a->S,
+                 "partial %d covers rows [%d, %d + %d) of %d", t, q.row_begin, q.row_begin, q.rows, a->S);
+    PITH_REQUIRE(q.rows == 0 || (q.o && q.lse), "partial %d: null tensor pointer", t);
+    PITH_REQUIRE(q.rows == 0 || rows_ok(q.o, q.o_stride, 2),
+                 "partial %d must be 16-byte aligned with 16-byte-multiple strides", t);
+    p.o[t] = static_cast<const __nv_bfloat16*>(q.o);
+    p.lse[t] = q.lse;
+    p.row_begin[t] = q.row_begin;
+    p.rows[t] = q.rows;
+    for (int i = 0; i < 3; ++i) p.os[t][i] = q.o_stride[i];
+    for (int i = 0; i < 2; ++i) p.ls[t][i] = q.lse_stride[i];
+  }
+  if (int rc = require_sm100()) return rc;
+  p.n = a->n;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.lse_out = a->lse;
+  p.B = a->B; p.S = a->S; p.H = a->H; p.D = a->D;
+  const int64_t items = static_cast<int64_t>(a->B) * a->S * a->H * (a->D / 8);
+  PITH_REQUIRE(a->H <= 65535 && a->B <= 65535 && items / a->H / a->B < (1ll << 32), "tensor too large for one launch");
+  combine_partials_kernel<<<grid_for(static_cast<int64_t>(a->S) * (a->D / 8), a->H, a->B), 256, 0,
+                            static_cast<cudaStream_t>(stream)>>>(p);
   PITH_CUDA(cudaGetLastError());
   return kOk;
 }

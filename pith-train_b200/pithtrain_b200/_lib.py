@@ -63,6 +63,24 @@ class CombineArgs(Structure):
     ]
 
 
+MAX_PARTIALS = 16
+
+
+class Partial(Structure):
+    _fields_ = [
+        ("o", c_void_p), ("lse", c_void_p), ("row_begin", c_int32), ("rows", c_int32),
+        ("o_stride", I64x3), ("lse_stride", I64x2),
+    ]
+
+
+class CombinePartialsArgs(Structure):
+    _fields_ = [
+        ("part", Partial * MAX_PARTIALS), ("n", c_int32),
+        ("B", c_int32), ("S", c_int32), ("H", c_int32), ("D", c_int32),
+        ("out", c_void_p), ("lse", c_void_p),
+    ]
+
+
 class AttnBwdNoallocArgs(Structure):
     _fields_ = [
         ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("o", c_void_p), ("dout", c_void_p), ("lse", c_void_p),
@@ -123,6 +141,7 @@ EXPORTS = {
     "pith_cast_f32_to_bf16": (c_int, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                       POINTER(c_int64), POINTER(c_int64), c_float, c_void_p]),
     "pith_combine": (c_int, [POINTER(CombineArgs), c_void_p]),
+    "pith_combine_partials": (c_int, [POINTER(CombinePartialsArgs), c_void_p]),
     "pith_attn_bwd_noalloc": (c_int, [POINTER(AttnBwdNoallocArgs), c_void_p]),
     "pith_attn_bwd_noalloc_scratch_bytes": (ctypes.c_size_t, [c_int32] * 7),
     "pith_flag_signal": (c_int, [c_void_p, c_void_p, c_void_p]),

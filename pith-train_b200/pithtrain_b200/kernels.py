@@ -270,6 +270,37 @@ def combine(out1, lse1, out2, lse2, natural: bool):
     return out, lse
 
 
+def combine_partials(parts, B: int, S: int, H: int, D: int):
+    """Merges partial attention results in one pass; see ``pith_combine_partials``.
+
+    ``parts``: sequence of ``(o, lse, row_begin)`` with ``o`` bf16 [B, rows, H, D] and ``lse`` fp32 [B, H, rows] (log2
+    domain), the partial result of query rows ``row_begin .. row_begin + rows`` over one K/V block.
+    Returns (bf16 out [B, S, H, D], fp32 lse [B, H, S])."""
+    parts = list(parts)
+    if not 1 <= len(parts) <= _lib.MAX_PARTIALS:
+        raise ValueError(f"combine_partials takes 1 .. {_lib.MAX_PARTIALS} partial results, got {len(parts)}")
+    _require_cuda(*[t for o, l, _ in parts for t in (o, l)])
+    dev = parts[0][0].device
+    out = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=dev)
+    a = _lib.CombinePartialsArgs()
+    a.n = len(parts)
+    a.B, a.S, a.H, a.D = B, S, H, D
+    a.out, a.lse = out.data_ptr(), lse.data_ptr()
+    for i, (o, l, row_begin) in enumerate(parts):
+        if o.dtype != torch.bfloat16:
+            raise TypeError(f"partial {i} must be bfloat16")
+        _expect(o, (B, o.shape[1], H, D), f"partial {i}")
+        _expect(l, (B, H, o.shape[1]), f"lse of partial {i}")
+        pt = a.part[i]
+        pt.o, pt.lse = o.data_ptr(), l.data_ptr()
+        pt.row_begin, pt.rows = int(row_begin), int(o.shape[1])
+        pt.o_stride, pt.lse_stride = _bshd(o, f"partial {i}"), _bhs(l, f"lse of partial {i}")
+    _lib.check(_lib.load().pith_combine_partials(ctypes.byref(a), _stream(out)), "pith_combine_partials")
+    _count(1 if out.numel() else 0)
+    return out, lse
+
+
 def _qk_args(q, k, q_weight, k_weight, cos, sin, eps):
     _require_cuda(q, k, q_weight, k_weight, cos, sin)
     B, S, Hq, D = q.shape

@@ -6,8 +6,9 @@ The schedule is the reference's (pithtrain/operators/ring_attention/standard.py:
 * the exchange of step ``t+1`` is issued BEFORE the attention kernel of step ``t`` and joined after
   it, so NCCL's copy over NVLink (on the process group's own stream) runs under the tensor-core work
   instead of after it (the reference waits on the requests right away, standard.py:46-50);
-* partial results are merged inside the attention kernel's epilogue into one fp32 running (O, LSE)
-  instead of ~10 elementwise kernels per step (standard.py:53-66, :94);
+* every step writes its own bf16 partial (O, LSE) and one kernel merges all of them at the end (LSE-weighted mean in
+  fp32, rounded once) instead of ~10 elementwise kernels per step (standard.py:53-66, :94). Rings longer than that
+  kernel takes, and backends without it, merge inside the attention kernel's epilogue into an fp32 running (O, LSE);
 * the backward circulates K/V again together with a travelling fp32 dK/dV accumulator that visits
   every rank and is home after ``cp_size`` hops, instead of keeping every visited K/V block alive
   and redistributing dK/dV by distance afterwards (standard.py:97-99, :164-187). Gradients are
@@ -71,6 +72,12 @@ class CudaBlockBackend:
 
     def cast(self, acc):
         return self.k.cast_to_bf16(acc)
+
+    max_partials = 16
+
+    def combine_partials(self, parts, B, S, H, D):
+        """``parts``: (O bf16 [B,rows,H,D], LSE [B,H,rows], first row) per ring step -> (O bf16 [B,S,H,D], LSE)."""
+        return self.k.combine_partials(parts, B, S, H, D)
 
     def bwd_single(self, q, k, v, do, lse, delta, scale, dk_acc, dv_acc):
         """The whole backward is this one causal block (CP = 1): returns dQ. At head_dim 128 the dQ pass stores its
@@ -150,6 +157,31 @@ def ring_forward(backend, comm: RingComm, q, k, v, scale: float, cp_rank: int, c
     c = S // 2
     _begin(comm, 2 * (k.numel() + v.numel()) * k.element_size())
     bufs, nk = _pack_kv(comm, k, v)
+    # One partial per step, merged after the last one: the attention kernels then store bf16 rows and nothing else (the
+    # fp32 merge in their epilogue costs a quarter of a 4096 x 2048 step: 160 us against 127 us).
+    lazy = hasattr(backend, "combine_partials") and cp_size <= getattr(backend, "max_partials", 0) and \
+        q.dtype == torch.bfloat16
+    if lazy:
+        parts = []
+        cur = 0
+        for t in range(cp_size):
+            kind = sh.step_kind(sharding, cp_rank, (cp_rank - t) % cp_size)
+            with _Range(f"ring_attn.f.step{t}.{kind}", q.is_cuda):
+                reqs = comm.exchange(bufs[cur], bufs[cur ^ 1]) if t < cp_size - 1 else None
+                kc, vc = _views(bufs[cur], nk, k.shape, v.shape)
+                if kind != sh.STEP_SKIP:
+                    row0 = c if kind == sh.STEP_Q_SECOND_HALF else 0
+                    po = torch.empty((B, S - row0, Hq, Dv), dtype=torch.bfloat16, device=q.device)
+                    pl = torch.empty((B, Hq, S - row0), dtype=torch.float32, device=q.device)
+                    if kind == sh.STEP_KV_FIRST_HALF:
+                        kc, vc = kc[:, :c], vc[:, :c]
+                    backend.fwd_block(q[:, row0:], kc, vc, scale, kind == sh.STEP_CAUSAL, po, pl, False)
+                    parts.append((po, pl, row0))
+                if reqs is not None:
+                    comm.wait(reqs)
+                    cur ^= 1
+        with _Range("ring_attn.f.merge", q.is_cuda):
+            return backend.combine_partials(parts, B, S, Hq, Dv)
     acc = torch.empty((B, S, Hq, Dv), dtype=torch.float32, device=q.device)
     cur = 0
     for t in range(cp_size):

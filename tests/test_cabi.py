@@ -43,9 +43,9 @@ def test_struct_sizes_match_the_header(built_library):
         #include <stdio.h>
         #include "pith_b200.h"
         int main(void) {
-          printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
+          printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(pith_attn_fwd_args), sizeof(pith_bwd_preprocess_args),
                  sizeof(pith_attn_bwd_args), sizeof(pith_combine_args), sizeof(pith_attn_bwd_noalloc_args),
-                 sizeof(pith_qk_norm_rope_args), sizeof(pith_mla_assemble_args));
+                 sizeof(pith_qk_norm_rope_args), sizeof(pith_mla_assemble_args), sizeof(pith_combine_partials_args));
           return 0;
         }""")
     with tempfile.TemporaryDirectory() as d:
@@ -55,7 +55,7 @@ def test_struct_sizes_match_the_header(built_library):
     assert sizes == [ctypes.sizeof(_lib.AttnFwdArgs), ctypes.sizeof(_lib.BwdPreprocessArgs),
                      ctypes.sizeof(_lib.AttnBwdArgs), ctypes.sizeof(_lib.CombineArgs),
                      ctypes.sizeof(_lib.AttnBwdNoallocArgs), ctypes.sizeof(_lib.QkNormRopeArgs),
-                     ctypes.sizeof(_lib.MlaAssembleArgs)]
+                     ctypes.sizeof(_lib.MlaAssembleArgs), ctypes.sizeof(_lib.CombinePartialsArgs)]
 
 
 def test_host_side_rejections(built_library):

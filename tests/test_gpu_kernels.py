@@ -158,6 +158,40 @@ def test_combine_golden(K, cuda_device):
             assert torch.allclose(lse, t[f"lse_{suffix}"], atol=1e-5, equal_nan=True)
 
 
+def test_combine_partials_matches_pairwise_oracle(K, cuda_device):
+    """The one-pass merge of the forward ring: partials that cover different row ranges (the zigzag steps), rows that
+    saw no key in some partials (LSE = -inf) or in all of them, against the oracle's pairwise combine in fp32."""
+    B, S, H, D = 2, 300, 3, 128
+    g = torch.Generator().manual_seed(11)
+    spans = [(0, S), (0, S), (150, S - 150), (150, S - 150), (0, S)]
+    parts = []
+    for i, (r0, rows) in enumerate(spans):
+        o = torch.randn(B, rows, H, D, generator=g).bfloat16()
+        l = torch.randn(B, H, rows, generator=g) * 3
+        if i == 1:
+            l[:, :, :40] = -math.inf       # these rows saw no key in this partial
+        if i != 2 and i != 3:
+            l[:, 1, 7] = -math.inf         # row 7 of head 1: no key anywhere (partials 2, 3 do not cover it)
+        parts.append((o, l, r0))
+    out, lse = K.combine_partials([(o.to(cuda_device), l.to(cuda_device), r0) for o, l, r0 in parts], B, S, H, D)
+    K.check_device_status(cuda_device)
+    ref_o = torch.zeros(B, S, H, D)
+    ref_l = torch.full((B, H, S), -math.inf)
+    for o, l, r0 in parts:
+        rows = o.shape[1]
+        old_l = ref_l[:, :, r0:r0 + rows]
+        co, cl = O.combine(ref_o[:, r0:r0 + rows], old_l, o.float(), l, log2=True)
+        dead = (old_l == -math.inf) & (l == -math.inf)          # both sides empty (the formula gives NaN): zeros, -inf
+        co = torch.where(dead.permute(0, 2, 1).unsqueeze(-1), torch.zeros_like(co), co)
+        cl = torch.where(dead, torch.full_like(cl, -math.inf), cl)
+        ref_o[:, r0:r0 + rows] = co
+        ref_l[:, :, r0:r0 + rows] = cl
+    assert out.dtype == torch.bfloat16 and lse.dtype == torch.float32
+    assert_bf16_close(out, ref_o, "combined O", max_abs=1e-2)
+    assert_lse_close(lse, ref_l)
+    assert (out[:, 7, 1] == 0).all() and torch.isinf(lse[:, 1, 7]).all()
+
+
 def test_combine_two_halves_identity_commutativity(cuda_device):
     from pithtrain_b200.operators.mla import _mla_fwd
     from pithtrain_b200.operators.ring_attention import _online_softmax_combine, _online_softmax_combine_log2
