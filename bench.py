@@ -663,9 +663,13 @@ class Bench:
         # ---- HBM-bound kernels of the path, timed alone: algorithmic bytes / time against the measured copy bandwidth
         n_row = S_loc * Hq
         acc_f32 = torch.randn(1, S_loc, Hq, Dv, device=dev)
+        parts8 = [(torch.randn(1, S_loc, Hq, Dv, device=dev).bfloat16(), torch.randn(1, Hq, S_loc, device=dev), 0)
+                  for _ in range(8)]  # eight distinct partial results, as the forward ring leaves them at CP = 8
         hbm_runs = {
             "combine_kernel (fp32 + bf16 -> fp32, log2)": (
                 lambda: kernels.combine(acc_f32, lse_d, out_d, lse_d, natural=False), n_row * Dv * (4 + 2 + 4) + 12 * n_row),
+            "combine_partials_kernel (8 x bf16 -> bf16, log2)": (
+                lambda: kernels.combine_partials(parts8, 1, S_loc, Hq, Dv), 9 * n_row * (Dv * 2 + 4)),
             "delta_kernel": (lambda: kernels.bwd_preprocess(out_d, do, delta_d), n_row * Dv * 4 + 4 * n_row),
             "cast_kernel (dQ)": (lambda: kernels.cast_to_bf16(dq_acc), n_row * Dqk * 6),
         }
