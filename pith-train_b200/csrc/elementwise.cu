@@ -99,8 +99,9 @@ struct PartialsParams {
   int B, S, H, D;
 };
 
-// One pass over the output: a thread owns 8 columns of a row, reads the LSEs of the partials that cover the row
-// (once for the maximum, once with the data), and writes the weighted mean as bf16.
+// One pass over the output: a thread owns 8 columns of a row. The LSEs of all partials are loaded first (one
+// register each), then the rows of eight partials at a time, so that up to eight 16-byte loads per thread are in
+// flight; the weighted mean is written as bf16.
 __global__ void __launch_bounds__(256) combine_partials_kernel(const __grid_constant__ PartialsParams p) {
   const uint32_t chunks = static_cast<uint32_t>(p.D) >> 3;
   const uint32_t plane = static_cast<uint32_t>(p.S) * chunks;
@@ -111,23 +112,41 @@ __global__ void __launch_bounds__(256) combine_partials_kernel(const __grid_cons
   for (uint32_t item = blockIdx.x * 256u + threadIdx.x; item < plane; item += gridDim.x * 256u) {
     const int s = static_cast<int>(item / chunks);
     const uint32_t d0 = (item - static_cast<uint32_t>(s) * chunks) << 3;
-    float mx = -INFINITY;
-    for (int t = 0; t < p.n; ++t) {
+    float l[PITH_MAX_PARTIALS];
+#pragma unroll
+    for (int t = 0; t < PITH_MAX_PARTIALS; ++t) {
       const int r = s - p.row_begin[t];
-      if (r >= 0 && r < p.rows[t]) mx = fmaxf(mx, __ldg(p.lse[t] + b * p.ls[t][0] + h * p.ls[t][1] + r));
+      l[t] = -INFINITY;
+      if (t < p.n && r >= 0 && r < p.rows[t]) l[t] = __ldg(p.lse[t] + b * p.ls[t][0] + h * p.ls[t][1] + r);
     }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < PITH_MAX_PARTIALS; ++t) mx = fmaxf(mx, l[t]);
     float den = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (mx > -INFINITY) {
-      for (int t = 0; t < p.n; ++t) {
-        const int r = s - p.row_begin[t];
-        if (r < 0 || r >= p.rows[t]) continue;
-        const float l = __ldg(p.lse[t] + b * p.ls[t][0] + h * p.ls[t][1] + r);
-        if (l == -INFINITY) continue;
-        const float w = exp2f(l - mx);
-        const Vec8 a = load8<false>(p.o[t], b * p.os[t][0] + r * p.os[t][1] + h * p.os[t][2] + d0);
-        den += w;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, a.v[i], acc[i]);
+      for (int g = 0; g < PITH_MAX_PARTIALS; g += 8) {
+        if (g >= p.n) break;
+        uint4 raw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int t = g + j;
+          raw[j] = make_uint4(0u, 0u, 0u, 0u);
+          if (l[t] > -INFINITY)  // implies t < n and the row is covered
+            raw[j] = __ldg(reinterpret_cast<const uint4*>(
+                p.o[t] + b * p.os[t][0] + static_cast<int64_t>(s - p.row_begin[t]) * p.os[t][1] + h * p.os[t][2] + d0));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float w = l[g + j] > -INFINITY ? exp2f(l[g + j] - mx) : 0.f;
+          den += w;
+          const uint32_t u[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = fmaf(w, __uint_as_float(u[i] << 16), acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, __uint_as_float(u[i] & 0xFFFF0000u), acc[2 * i + 1]);
+          }
+        }
       }
     }
     const float inv = den > 0.f ? 1.0f / den : 0.f;
@@ -269,7 +288,7 @@ extern "C" int pith_combine_partials(const pith_combine_partials_args* a, void* 
                a->H, a->D);
   if (static_cast<int64_t>(a->B) * a->S * a->H == 0) return kOk;
   PITH_REQUIRE(a->out && a->lse && aligned16(a->out), "out must be a 16-byte aligned pointer, lse non-null");
-  PartialsParams p;
+  PartialsParams p = {};
   for (int t = 0; t < a->n; ++t) {
     const pith_partial& q = a->part[t];
     PITH_REQUIRE(q.rows >= 0 && q.row_begin >= 0 && static_cast<int64_t>(q.row_begin) + q.rows <= a->S,
