@@ -4,7 +4,9 @@
 // One CTA owns two 128-row query tiles of one (batch, query head) and walks the key/value
 // blocks they need. Warp roles (384 threads):
 //   warp 0        TMA producer: Q once, then K and V blocks through KST / VST-deep rings
-//   warp 1        tcgen05 issuer (one lane): S_t = Q_t K_j^T, O_t += P_t V_j
+//   warp 1        tcgen05 issuer (the warp walks the loop converged, one elected lane issues):
+//                 S_t = Q_t K_j^T, O_t += P_t V_j; the PV GEMM starts on the first 64 keys' P while the second
+//                 64 are still being exponentiated
 //   warps 4..7    softmax group of tile 0, one thread per query row (= TMEM lane)
 //   warps 8..11   softmax group of tile 1
 // The two softmax groups alternate with the tensor core: while group 0 turns S_0 into P_0
@@ -16,7 +18,8 @@
 // Softmax runs in the exp2 domain; the running maximum is only moved when it grows by more than
 // 2^8 (warp-uniform decision), which keeps the O rescale off the common path. The epilogue
 // normalises, optionally merges a previous partial (O, LSE) (the ring's online-softmax combine)
-// and writes bf16 or fp32 O plus the log2-domain LSE.
+// and writes bf16 or fp32 O plus the log2-domain LSE. Causal launches take their (tile, head) from launch_order()
+// (heads in groups of eight, heaviest tiles first).
 #include "attn_fwd_common.cuh"
 
 namespace pith {

@@ -1,11 +1,13 @@
 // Attention forward on CTA pairs (sm_100a, tcgen05 with cta_group::2).
 //
-// A single-CTA forward reads, per K/V block, 128 KB of Q/K operands and 64 KB of V from shared memory and takes
-// 64 KB of TMA writes for 2048 tensor cycles: more than one SM's shared memory delivers, so the tensor pipe idles.
-// Here two CTAs (a cluster of 2) run every MMA together: the accumulator has 256 rows, 128 in each CTA's TMEM,
-// each CTA supplies its own 128 rows of the A operand (Q from its shared memory, P from its TMEM) and only HALF of
-// the B operand: 64 of the block's 128 keys for S = Q K^T, 64 of the 128 value columns for O += P V. Per CTA and
-// K/V block that is 96 + 32 KB of operand reads and 32 KB of TMA writes for the same 2048 tensor cycles.
+// Two CTAs (a cluster of 2) run every MMA together: the accumulator has 256 rows, 128 in each CTA's TMEM, each CTA
+// supplies its own 128 rows of the A operand (Q from its shared memory, P from its TMEM) and only HALF of the B
+// operand: 64 of the block's 128 keys for S = Q K^T, 64 of the 128 value columns for O += P V. What that buys is
+// capacity, not MMA rate (a cta_group::2 MMA costs the same 64 cycles per K-step as a single-CTA one, and the single-CTA
+// kernel is not short of shared-memory bandwidth): K/V stages are half as large, so the 192-wide MLA heads get a
+// second V stage that does not fit next to 96 KB of Q in one CTA, and the L2 -> SM stream per CTA halves. Measured:
+// faster for Dqk = 192 (0.338 -> 0.269 ms at 16 heads x 8192^2 causal), slower for Dqk = 128 (0.431 -> 0.477 ms),
+// which therefore stays on the single-CTA kernel.
 //
 // A pair owns 512 consecutive query rows of one (batch, head): CTA c holds rows [(2t + c) * 128, +128) as its
 // tile t (t = 0, 1), so that tile t of both CTAs forms one 256-row MMA. Warp roles as in the single-CTA kernel
