@@ -74,6 +74,7 @@ class CudaBlockBackend:
         return self.k.cast_to_bf16(acc)
 
     max_partials = 16
+    partial_dtype = torch.bfloat16
 
     def combine_partials(self, parts, B, S, H, D):
         """``parts``: (O bf16 [B,rows,H,D], LSE [B,H,rows], first row) per ring step -> (O bf16 [B,S,H,D], LSE)."""
@@ -159,9 +160,9 @@ def ring_forward(backend, comm: RingComm, q, k, v, scale: float, cp_rank: int, c
     bufs, nk = _pack_kv(comm, k, v)
     # One partial per step, merged after the last one: the attention kernels then store bf16 rows and nothing else (the
     # fp32 merge in their epilogue costs a quarter of a 4096 x 2048 step: 160 us against 127 us).
-    lazy = hasattr(backend, "combine_partials") and cp_size <= getattr(backend, "max_partials", 0) and \
-        q.dtype == torch.bfloat16
+    lazy = hasattr(backend, "combine_partials") and cp_size <= getattr(backend, "max_partials", 0)
     if lazy:
+        pdtype = getattr(backend, "partial_dtype", torch.bfloat16)
         parts = []
         cur = 0
         for t in range(cp_size):
@@ -171,7 +172,7 @@ def ring_forward(backend, comm: RingComm, q, k, v, scale: float, cp_rank: int, c
                 kc, vc = _views(bufs[cur], nk, k.shape, v.shape)
                 if kind != sh.STEP_SKIP:
                     row0 = c if kind == sh.STEP_Q_SECOND_HALF else 0
-                    po = torch.empty((B, S - row0, Hq, Dv), dtype=torch.bfloat16, device=q.device)
+                    po = torch.empty((B, S - row0, Hq, Dv), dtype=pdtype, device=q.device)
                     pl = torch.empty((B, Hq, S - row0), dtype=torch.float32, device=q.device)
                     if kind == sh.STEP_KV_FIRST_HALF:
                         kc, vc = kc[:, :c], vc[:, :c]

@@ -88,6 +88,34 @@ class OracleBlockBackend:
         return acc.clone()
 
 
+class OraclePartialsBackend(OracleBlockBackend):
+    """The same, offering the one-pass merge of per-step partial results that the forward ring prefers."""
+
+    max_partials = 16
+
+    def __init__(self, dtype=torch.float32):
+        super().__init__(dtype)
+        self.partial_dtype = dtype
+        self.merges = 0
+
+    def fwd_block(self, q, k, v, scale, causal, out, lse, merge):
+        assert not merge, "with combine_partials on offer the ring must not merge in the block"
+        super().fwd_block(q, k, v, scale, causal, out, lse, False)
+
+    def combine_partials(self, parts, B, S, H, D):
+        self.merges += 1
+        out = torch.zeros((B, S, H, D), dtype=self.dtype)
+        lse = torch.full((B, H, S), -float("inf"), dtype=self.dtype)
+        for o, l, r0 in parts:
+            rows = o.shape[1]
+            old = lse[:, :, r0:r0 + rows]
+            co, cl = O.combine(out[:, r0:r0 + rows], old, o.to(self.dtype), l.to(self.dtype), log2=True)
+            dead = torch.isinf(old) & torch.isinf(l.to(self.dtype))  # both sides saw no key: the formula gives NaN
+            out[:, r0:r0 + rows] = torch.where(dead.permute(0, 2, 1).unsqueeze(-1), torch.zeros_like(co), co)
+            lse[:, :, r0:r0 + rows] = torch.where(dead, torch.full_like(cl, -float("inf")), cl)
+        return out, lse.float() if self.dtype != torch.float64 else lse
+
+
 class ThreadRing:
     """In-process stand-in for the ring's P2P: ``cp_size`` threads, one per simulated rank, exchanging
     tensors through mailboxes. Lets the schedule (and on a GPU the real kernels) run on a single device.

@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from helpers import LazyPullRing, OracleBlockBackend, ThreadRing
+from helpers import LazyPullRing, OracleBlockBackend, OraclePartialsBackend, ThreadRing
 from oracle import attention_oracle as O
 from pithtrain_b200.operators.ring_attention import _ring
 from pithtrain_b200.operators.ring_attention import sharding as sh
@@ -49,6 +49,28 @@ def test_schedule_in_process(cp, layout):
     ring = ThreadRing(cp)
     res = ring.run(lambda r, comm: _rank_fwd_bwd(r, cp, comm, layout, q, k, v, do, 0.25, torch.float64))
     _check_against_full(res, cp, layout, q, k, v, do, 0.25, 5e-6)
+
+
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+@pytest.mark.parametrize("cp", [2, 3, 8])
+def test_forward_with_one_pass_merge(cp, layout):
+    """A backend that offers ``combine_partials`` gets one un-merged partial per visible step (the zigzag
+    ``q_second_half`` steps cover the second half of the rows only, contiguous ``skip`` steps none) and one merge."""
+    S = 16 * cp * 2
+    q, k, v, do = _problem(S, dtype=torch.float64)
+    ring = ThreadRing(cp)
+    backends = [OraclePartialsBackend(torch.float64) for _ in range(cp)]
+
+    def rank(r, comm):
+        loc = lambda t: sh.shard_sequence(t, cp, r, layout).contiguous()  # noqa: E731
+        return _ring.ring_forward(backends[r], comm, loc(q), loc(k), loc(v), 0.25, r, cp, layout)
+
+    res = ring.run(rank)
+    full = O.full_attention_fwd_bwd(q, k, v, do, 0.25, torch.float64)
+    for name, i, dim in (("o", 0, 1), ("lse_log2", 1, 2)):
+        got = sh.unshard_sequence([x[i].double() for x in res], layout, seq_dim=dim)
+        assert torch.allclose(got, full[name], atol=5e-6), (layout, cp, name, (got - full[name]).abs().max())
+    assert all(b.merges == 1 for b in backends)
 
 
 @pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
