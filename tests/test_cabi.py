@@ -82,6 +82,19 @@ def test_host_side_rejections(built_library):
     e = _lib.CombineArgs()
     e.B, e.S, e.H, e.D = 1, 0, 2, 128
     assert lib.pith_combine(ctypes.byref(e), None) == 0  # empty input: nothing to do, null pointers accepted
+    cp = _lib.CombinePartialsArgs()
+    cp.B, cp.S, cp.H, cp.D = 1, 256, 2, 128
+    assert lib.pith_combine_partials(ctypes.byref(cp), None) < 0 and b"partials" in lib.pith_last_error()  # n = 0
+    cp.n = _lib.MAX_PARTIALS + 1
+    assert lib.pith_combine_partials(ctypes.byref(cp), None) < 0 and b"partials" in lib.pith_last_error()
+    cp.n = 1
+    cp.out = cp.lse = 0x1000
+    cp.part[0].row_begin, cp.part[0].rows = 128, 256                       # runs past the 256 output rows
+    assert lib.pith_combine_partials(ctypes.byref(cp), None) < 0 and b"covers rows" in lib.pith_last_error()
+    cp.part[0].rows = 128
+    assert lib.pith_combine_partials(ctypes.byref(cp), None) < 0 and b"null tensor pointer" in lib.pith_last_error()
+    cp.S = 0
+    assert lib.pith_combine_partials(ctypes.byref(cp), None) == 0          # empty output: nothing to do
     b = _lib.AttnBwdArgs()
     b.q = b.k = b.v = b.dout = b.lse = b.delta = 0x1000
     assert lib.pith_attn_bwd(ctypes.byref(b), None) < 0
