@@ -99,19 +99,25 @@ struct PartialsParams {
   int B, S, H, D;
 };
 
-// One pass over the output: a thread owns 8 columns of a row. The LSEs of all partials are loaded first (one
-// register each), then the rows of eight partials at a time, so that up to eight 16-byte loads per thread are in
-// flight; the weighted mean is written as bf16.
+// One pass over the output: a thread owns 8 columns of a row. Rows are walked in storage order (s, then h), so every
+// partial and the output are streamed linearly (eight input streams: walking one head's rows, 8 KB apart, kept too
+// many DRAM pages open); the [B][H][S] LSEs are then read with a stride, but they are 1/64 of the bytes and every
+// sector serves eight consecutive rows. The LSEs of all partials are loaded first (one register each), then the rows
+// of eight partials at a time, so that up to eight 16-byte loads per thread are in flight; the weighted mean is
+// written as bf16. Grid (blocks per batch, 1, B).
 __global__ void __launch_bounds__(256) combine_partials_kernel(const __grid_constant__ PartialsParams p) {
   const uint32_t chunks = static_cast<uint32_t>(p.D) >> 3;
-  const uint32_t plane = static_cast<uint32_t>(p.S) * chunks;
-  const int h = blockIdx.y, b = blockIdx.z;
-  __nv_bfloat16* outp = p.out + (static_cast<int64_t>(b) * p.S * p.H + h) * p.D;
-  float* lsep = p.lse_out + (static_cast<int64_t>(b) * p.H + h) * p.S;
-  const int64_t out_row = static_cast<int64_t>(p.H) * p.D;
+  const uint32_t H = static_cast<uint32_t>(p.H);
+  const uint32_t plane = static_cast<uint32_t>(p.S) * H * chunks;
+  const int b = blockIdx.z;
+  __nv_bfloat16* outb = p.out + static_cast<int64_t>(b) * p.S * p.H * p.D;
+  float* lseb = p.lse_out + static_cast<int64_t>(b) * p.H * p.S;
   for (uint32_t item = blockIdx.x * 256u + threadIdx.x; item < plane; item += gridDim.x * 256u) {
-    const int s = static_cast<int>(item / chunks);
-    const uint32_t d0 = (item - static_cast<uint32_t>(s) * chunks) << 3;
+    const uint32_t row = item / chunks, d0 = (item - row * chunks) << 3;
+    const int s = static_cast<int>(row / H), h = static_cast<int>(row - static_cast<uint32_t>(s) * H);
+    __nv_bfloat16* outp = outb + static_cast<int64_t>(h) * p.D;
+    float* lsep = lseb + static_cast<int64_t>(h) * p.S;
+    const int64_t out_row = static_cast<int64_t>(p.H) * p.D;
     float l[PITH_MAX_PARTIALS];
 #pragma unroll
     for (int t = 0; t < PITH_MAX_PARTIALS; ++t) {
@@ -309,8 +315,8 @@ extern "C" int pith_combine_partials(const pith_combine_partials_args* a, void* 
   p.lse_out = a->lse;
   p.B = a->B; p.S = a->S; p.H = a->H; p.D = a->D;
   const int64_t items = static_cast<int64_t>(a->B) * a->S * a->H * (a->D / 8);
-  PITH_REQUIRE(a->H <= 65535 && a->B <= 65535 && items / a->H / a->B < (1ll << 32), "tensor too large for one launch");
-  combine_partials_kernel<<<grid_for(static_cast<int64_t>(a->S) * (a->D / 8), a->H, a->B), 256, 0,
+  PITH_REQUIRE(a->B <= 65535 && items / a->B < (1ll << 32), "tensor too large for one launch");
+  combine_partials_kernel<<<grid_for(static_cast<int64_t>(a->S) * a->H * (a->D / 8), 1, a->B), 256, 0,
                             static_cast<cudaStream_t>(stream)>>>(p);
   PITH_CUDA(cudaGetLastError());
   return kOk;
